@@ -1,0 +1,114 @@
+// Log-sum-exp merge of split-KV partial results.
+//
+// Math of csrc/smxx/mla_combine.cu:71-107, 128-151: with base-2 partial LSEs
+// lse_i and normalised partial outputs o_i,
+//   lse = log2(sum_i 2^lse_i)  (computed max-shifted; all -inf -> +inf),
+//   o   = sum_i 2^(lse_i - lse) * o_i,
+// written as natural-log LSE and bf16 O.  One warp per output row, any number of
+// parts (the reference is limited to 64, mla_combine.cu:156-167).  Each lane
+// owns 16 of the 512 output columns as 4 float4 so a warp reads 512 B
+// contiguous per load instruction.
+#include "fmla_common.cuh"
+#include "kernels.h"
+
+namespace fmla {
+
+constexpr int kCombineWarps = 8;
+
+// lse_part(i) / o_part(i) address part i of this row.
+template <class LseAt, class OAt>
+__device__ __forceinline__ void combine_row(int nparts, LseAt lse_at, OAt o_at, float* s_w, __nv_bfloat16* out_row,
+                                            float* lse_out) {
+  const int lane = threadIdx.x & 31;
+  float mx = neg_inf();
+  for (int i = lane; i < nparts; i += 32) mx = fmaxf(mx, lse_at(i));
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  if (mx == neg_inf()) mx = 0.f;
+  float sum = 0.f;
+  for (int i = lane; i < nparts; i += 32) sum += exp2f(lse_at(i) - mx);
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  const float glse = (sum == 0.f || sum != sum) ? pos_inf() : log2f(sum) + mx;
+  if (lane == 0) *lse_out = glse * kLn2;
+  for (int i = lane; i < nparts; i += 32) s_w[i] = exp2f(lse_at(i) - glse);
+  __syncwarp();
+
+  float4 acc[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int i = 0; i < nparts; ++i) {
+    const float w = s_w[i];
+    if (w == 0.f) continue;
+    const float4* src = reinterpret_cast<const float4*>(o_at(i));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float4 v = __ldg(src + j * 32 + lane);
+      acc[j].x += w * v.x;
+      acc[j].y += w * v.y;
+      acc[j].z += w * v.z;
+      acc[j].w += w * v.w;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint2 packed = make_uint2(pack_bf16x2(acc[j].x, acc[j].y), pack_bf16x2(acc[j].z, acc[j].w));
+    *reinterpret_cast<uint2*>(out_row + (j * 32 + lane) * 4) = packed;
+  }
+}
+
+// grid (b, ceil(h_k*q_seq_per_hk / 8)); requests with a single part were written
+// in final form by the attention kernel and are skipped (mla_combine.cu:30-32).
+__global__ void __launch_bounds__(kCombineWarps * 32) decode_combine_kernel(const __grid_constant__ DecodeKernelParams p) {
+  extern __shared__ float s_weights[];  // [8][num_sm_parts]
+  const int batch = blockIdx.x;
+  const int lo = __ldg(p.num_splits + batch), hi = __ldg(p.num_splits + batch + 1);
+  const int nparts = hi - lo;
+  if (nparts <= 1) return;
+  const int q_seq_per_hk = p.s_q * p.hq_per_hk;
+  const int rows = p.h_k * q_seq_per_hk;
+  const int warp = threadIdx.x >> 5;
+  const int r = blockIdx.y * kCombineWarps + warp;
+  if (r >= rows) return;
+  const int kh = r / q_seq_per_hk, row = r % q_seq_per_hk;
+  const int sq = row / p.hq_per_hk, head = kh * p.hq_per_hk + row % p.hq_per_hk;
+  const float* lse_base = p.lse_accum + (int64_t)lo * rows + r;
+  const float* o_base = p.o_accum + ((int64_t)lo * rows + r) * 512;
+  const int64_t part_stride = rows;
+  combine_row(
+      nparts, [&](int i) { return __ldg(lse_base + i * part_stride); },
+      [&](int i) { return o_base + i * part_stride * 512; }, s_weights + warp * p.num_sm_parts,
+      reinterpret_cast<__nv_bfloat16*>(p.out) + batch * p.o_stride_b + sq * p.o_stride_s + head * p.o_stride_h,
+      p.softmax_lse + ((int64_t)batch * p.h_q + head) * p.s_q + sq);
+}
+
+__global__ void __launch_bounds__(kCombineWarps * 32)
+combine_partials_kernel(const float* __restrict__ lse_accum, const float* __restrict__ o_accum, int nparts, int rows,
+                        __nv_bfloat16* __restrict__ out, int64_t o_stride_row, float* __restrict__ lse) {
+  extern __shared__ float s_weights[];  // [8][nparts]
+  const int warp = threadIdx.x >> 5;
+  const int r = blockIdx.x * kCombineWarps + warp;
+  if (r >= rows) return;
+  combine_row(
+      nparts, [&](int i) { return __ldg(lse_accum + (int64_t)i * rows + r); },
+      [&](int i) { return o_accum + ((int64_t)i * rows + r) * 512; }, s_weights + warp * nparts, out + r * o_stride_row,
+      lse + r);
+}
+
+cudaError_t launch_decode_combine(const DecodeKernelParams& p, cudaStream_t stream) {
+  const int rows = p.h_k * p.s_q * p.hq_per_hk;
+  dim3 grid(p.b, (rows + kCombineWarps - 1) / kCombineWarps);
+  const size_t smem = sizeof(float) * kCombineWarps * p.num_sm_parts;
+  decode_combine_kernel<<<grid, kCombineWarps * 32, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine_partials(const float* lse_accum, const float* o_accum, int num_parts, int rows, void* out,
+                                    int64_t o_stride_row, float* lse, cudaStream_t stream) {
+  const size_t smem = sizeof(float) * kCombineWarps * num_parts;
+  combine_partials_kernel<<<(rows + kCombineWarps - 1) / kCombineWarps, kCombineWarps * 32, smem, stream>>>(
+      lse_accum, o_accum, num_parts, rows, reinterpret_cast<__nv_bfloat16*>(out), o_stride_row, lse);
+  return cudaGetLastError();
+}
+
+}  // namespace fmla

@@ -1,0 +1,83 @@
+// Internal launcher declarations shared by the kernel translation units and the
+// C-ABI layer (abi.cu).  Kernel parameter blocks are plain structs passed by
+// value as __grid_constant__.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fmla {
+
+struct DecodeKernelParams {
+  int b, s_q, h_q, h_k, hq_per_hk;
+  int num_blocks;
+  int is_causal;
+  int topk;  // -1 dense
+  float scale_log2;
+  const void* q;
+  int64_t q_stride_b, q_stride_s, q_stride_h;
+  const void* kcache;
+  int64_t k_stride_block, k_stride_row, k_stride_head;  // elements (dense) / bytes (fp8)
+  const int* block_table;
+  int64_t block_table_stride_b;
+  const int* seqlens_k;
+  const int* indices;
+  int64_t indices_stride_b, indices_stride_s;
+  const int* tile_scheduler_metadata;
+  int num_sm_parts;
+  const int* num_splits;
+  void* out;
+  int64_t o_stride_b, o_stride_s, o_stride_h;
+  float* softmax_lse;
+  float* lse_accum;
+  float* o_accum;
+};
+
+struct SparsePrefillKernelParams {
+  int s_q, s_kv, h_q, topk;
+  float scale_log2;
+  const void* q;
+  int64_t q_stride_s, q_stride_h;
+  const void* kv;
+  int64_t kv_stride_s;
+  const int* indices;
+  int64_t indices_stride_s;
+  void* out;
+  float* max_logits;
+  float* lse;
+};
+
+struct DenseKernelParams {
+  int batch, h_q, h_k, d_qk, d_v, max_seqlen_q, max_seqlen_k, is_causal;
+  int total_q, total_k;
+  float scale, scale_log2;
+  const void* q; int64_t q_stride_t, q_stride_h;
+  const void* k; int64_t k_stride_t, k_stride_h;
+  const void* v; int64_t v_stride_t, v_stride_h;
+  const int* cu_q;
+  const int* cu_k;
+  void* o; int64_t o_stride_t, o_stride_h;
+  float* lse; int64_t lse_stride_t, lse_stride_h;
+  const void* d_o; int64_t do_stride_t, do_stride_h;
+  void* dq; int64_t dq_stride_t, dq_stride_h;
+  void* dk; int64_t dk_stride_t, dk_stride_h;
+  void* dv; int64_t dv_stride_t, dv_stride_h;
+  float* delta;      // workspace: [h_q, total_q] rowsum(dO * O)
+  float* dq_acc;     // workspace (unused by the deterministic dQ pass)
+};
+
+cudaError_t launch_get_mla_metadata(const int* seqlens_k, int batch, int num_sm_parts, int topk, int* md,
+                                    int* num_splits, cudaStream_t stream);
+cudaError_t launch_decode_mma(const DecodeKernelParams& p, cudaStream_t stream);
+// Merge of split partials for a decode call (reads num_splits; skips unsplit requests).
+cudaError_t launch_decode_combine(const DecodeKernelParams& p, cudaStream_t stream);
+// Stand-alone merge of num_parts partial slots for `rows` rows.
+cudaError_t launch_combine_partials(const float* lse_accum, const float* o_accum, int num_parts, int rows, void* out,
+                                    int64_t o_stride_row, float* lse, cudaStream_t stream);
+cudaError_t launch_sparse_prefill_mma(const SparsePrefillKernelParams& p, cudaStream_t stream);
+cudaError_t launch_dense_fwd_mma(const DenseKernelParams& p, cudaStream_t stream);
+cudaError_t launch_dense_bwd_mma(const DenseKernelParams& p, cudaStream_t stream);
+cudaError_t launch_quantize_kv_fp8(const void* kv, int64_t kv_stride_row, int num_tokens, const int* dst_slots,
+                                   void* cache, int64_t cache_stride_slot, cudaStream_t stream);
+
+}  // namespace fmla

@@ -1,0 +1,216 @@
+/*
+ * flashmla_b200 -- C ABI of the B200 (sm_100a) MLA attention library.
+ *
+ * This header is the whole boundary: plain pointers, sizes and strides, an
+ * `int` status return, caller-owned outputs and scratch, and the CUDA stream
+ * passed as an opaque pointer.  No torch / ATen type appears here.  Each entry
+ * point names the function of the reference extension (csrc/pybind.cpp, bound
+ * at :870-911) that it replaces.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer on the current device unless its name
+ *     ends in `_host`;
+ *   - strides are in ELEMENTS of the pointed-to type (bytes for the FP8 cache),
+ *     as in the reference's parameter blocks (csrc/params.h:5-49, pybind.cpp:553);
+ *   - functions only enqueue work on `stream` and return; they never call
+ *     exit() or trap the device (the reference does both, csrc/utils.h:3-45);
+ *   - return value 0 = FMLA_OK, otherwise an fmla_status code;
+ *     fmla_status_string() gives a static description and
+ *     fmla_last_error_message() a thread-local detailed message.
+ *   - thread safety: entry points may be called concurrently from different
+ *     host threads on different streams/devices; the library keeps no mutable
+ *     global state besides per-device attribute caches guarded by a mutex.
+ */
+#ifndef FLASHMLA_B200_H_
+#define FLASHMLA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum fmla_status {
+  FMLA_OK = 0,
+  FMLA_ERR_INVALID_ARGUMENT = 1,   /* shape / stride / pointer / alignment rejected */
+  FMLA_ERR_UNSUPPORTED = 2,        /* valid request the kernels do not implement   */
+  FMLA_ERR_CUDA = 3,               /* a CUDA runtime call failed (see message)      */
+  FMLA_ERR_WRONG_ARCH = 4,         /* device is not compute capability 10.x         */
+  FMLA_ERR_DEVICE_TIMEOUT = 5      /* a bounded device-side wait expired            */
+} fmla_status;
+
+enum { FMLA_TILE_SCHEDULER_METADATA_SIZE = 8 };  /* csrc/params.h:51 */
+enum { FMLA_DTYPE_BF16 = 0, FMLA_DTYPE_FP16 = 1 };
+
+const char* fmla_status_string(int status);
+const char* fmla_last_error_message(void);
+/* Library version "major.minor.patch" and the variant string the Python layer
+ * reports as FLASH_MLA_LOADED_VARIANT (flash_mla/flash_mla_interface.py:54). */
+const char* fmla_version(void);
+const char* fmla_variant(void);
+
+/* ------------------------------------------------------------------------- *
+ * Split-KV tile scheduler.
+ * Replaces get_mla_decoding_metadata (csrc/pybind.cpp:383-428), i.e.
+ * get_attn_impl_meta (:288-380) + run_get_mla_metadata_kernel
+ * (csrc/smxx/get_mla_metadata.cu:8-96).
+ * ------------------------------------------------------------------------- */
+
+/* Host query: how many partitions the schedule has for this problem on
+ * `device` (so the caller can size tile_scheduler_metadata).
+ *   num_q_tokens_per_head_k = s_q * h_q / h_k;  h_q is needed only when
+ *   is_sparse != 0;  is_fp8_kvcache must equal is_sparse (dense FP8 and sparse
+ *   BF16 caches are rejected, as in pybind.cpp:312-355). */
+int fmla_get_num_sm_parts(int device, int num_q_tokens_per_head_k, int h_k, int h_q,
+                          int is_fp8_kvcache, int is_sparse, int* num_sm_parts_host);
+
+/* Enqueue the scheduler.  seqlens_k [batch] int32;  topk = -1 for dense
+ * attention, otherwise every request is scheduled with length topk
+ * (get_mla_metadata.cu:27).  Outputs:
+ *   tile_scheduler_metadata [num_sm_parts][8] int32 =
+ *     {begin_idx, begin_block_idx, end_idx (inclusive), end_block_idx
+ *      (exclusive), begin_n_split_idx, 0, 0, 0}            (csrc/params.h:52)
+ *   num_splits [batch+1] int32, exclusive prefix of per-request part counts. */
+int fmla_get_mla_metadata(const int32_t* seqlens_k, int batch, int num_sm_parts, int topk,
+                          int32_t* tile_scheduler_metadata, int32_t* num_splits, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Decode attention over a paged KV cache (dense BF16, or sparse FP8 + top-k).
+ * Replaces fwd_kvcache_mla (csrc/pybind.cpp:430-720): split-KV attention
+ * kernel followed by the log-sum-exp combine (csrc/smxx/mla_combine.cu).
+ * Mirrors DecodingParams (csrc/params.h:5-49); outputs and scratch are
+ * caller-allocated (the reference allocates them at pybind.cpp:526-528, 574-581).
+ * ------------------------------------------------------------------------- */
+typedef struct fmla_decode_params {
+  int32_t b, s_q, h_q, h_k;        /* batch, queries per request, q heads, kv heads */
+  int32_t d, d_v;                  /* 576, 512                                       */
+  int32_t num_blocks;              /* pages in the cache                             */
+  int32_t page_block_size;         /* 64                                             */
+  int32_t is_causal;               /* ignored when s_q == 1 (pybind.cpp:501)         */
+  int32_t is_fp8;                  /* cache holds 656-byte FP8 token records         */
+  int32_t topk;                    /* -1 = dense; else indices[...,topk] are used    */
+  int32_t q_dtype;                 /* FMLA_DTYPE_BF16                                */
+  float softmax_scale;
+
+  const void* q;                   /* [b, s_q, h_q, d]; last dim contiguous          */
+  int64_t q_stride_b, q_stride_s, q_stride_h;
+  const void* kcache;              /* bf16 [num_blocks, 64, h_k, d]  or  bytes [num_blocks, 64, 1, 656] */
+  int64_t k_stride_block, k_stride_row, k_stride_head;
+  const int32_t* block_table;      /* [b, max_blocks]; dense only                    */
+  int64_t block_table_stride_b;
+  const int32_t* seqlens_k;        /* [b]                                            */
+  const int32_t* indices;          /* [b, s_q, topk] physical slots page*64+off, <0 or >= num_blocks*64 = padding */
+  int64_t indices_stride_b, indices_stride_s;
+
+  const int32_t* tile_scheduler_metadata;  /* from fmla_get_mla_metadata             */
+  int32_t num_sm_parts;
+  const int32_t* num_splits;       /* [b+1]                                          */
+
+  void* out;                       /* [b, s_q, h_q, d_v] q dtype; last dim contiguous */
+  int64_t o_stride_b, o_stride_s, o_stride_h;
+  float* softmax_lse;              /* [b, h_q, s_q] contiguous, natural log, +inf for empty rows */
+
+  /* scratch for split requests: (b + num_sm_parts) partial slots, see
+   * fmla_decode_scratch_bytes(); contents on entry are irrelevant. */
+  float* lse_accum;                /* [b + num_sm_parts, h_k, s_q*h_q/h_k]           */
+  float* o_accum;                  /* [b + num_sm_parts, h_k, s_q*h_q/h_k, d_v]      */
+
+  /* optional cudaEvent_t pair recorded on `stream` immediately before and after
+   * the attention kernel (the combine kernel follows the second); NULL = off. */
+  void* profile_event_begin;
+  void* profile_event_end;
+} fmla_decode_params;
+
+/* Bytes of lse_accum and o_accum for a problem (host-side arithmetic only). */
+int fmla_decode_scratch_bytes(int b, int s_q, int h_q, int num_sm_parts, int d_v,
+                              size_t* lse_accum_bytes_host, size_t* o_accum_bytes_host);
+
+int fmla_fwd_kvcache_mla(const fmla_decode_params* params_host, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Stand-alone log-sum-exp merge of normalised partial results.
+ * Replaces run_flash_mla_combine_kernel (csrc/smxx/mla_combine.cu:170-195) and
+ * lifts its 64-split limit (:156-167).  Also the merge step of a KV-sharded
+ * decode across GPUs: partials written by peers into this GPU's memory are
+ * merged exactly like local split-KV partials.
+ *   lse_accum [num_parts, rows] base-2 (-inf = empty), o_accum [num_parts, rows, d_v] fp32
+ *   out [rows, d_v] bf16 (row stride o_stride_row), lse [rows] natural log.
+ * ------------------------------------------------------------------------- */
+int fmla_combine_partials(const float* lse_accum, const float* o_accum, int num_parts, int rows,
+                          int d_v, void* out, int64_t o_stride_row, float* lse, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Sparse MLA prefill forward.  Replaces sparse_prefill_fwd
+ * (csrc/pybind.cpp:730-814) -> sm100::run_fwd_kernel
+ * (csrc/sm100/prefill/sparse/fwd.cu:705-783).  Mirrors SparsePrefillParams
+ * (csrc/params.h:65-84).  Requires h_kv == 1, d_qk == 576, d_v == 512,
+ * h_q % 64 == 0, topk % 64 == 0.
+ * ------------------------------------------------------------------------- */
+typedef struct fmla_sparse_prefill_params {
+  int32_t s_q, s_kv, h_q, h_kv, d_qk, d_v, topk;
+  float sm_scale;
+  const void* q;          int64_t q_stride_s, q_stride_h;        /* bf16 [s_q, h_q, d_qk]  */
+  const void* kv;         int64_t kv_stride_s, kv_stride_h;      /* bf16 [s_kv, h_kv, d_qk] */
+  const int32_t* indices; int64_t indices_stride_s, indices_stride_h;  /* [s_q, h_kv, topk]; <0 or >= s_kv = padding */
+  void* out;              /* bf16 [s_q, h_q, d_v] contiguous */
+  float* max_logits;      /* [s_q, h_q], base-2 logits' maximum, -inf for empty rows */
+  float* lse;             /* [s_q, h_q], base-2 log-sum-exp, -inf for empty rows      */
+} fmla_sparse_prefill_params;
+
+int fmla_sparse_prefill_fwd(const fmla_sparse_prefill_params* params_host, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Dense variable-length MHA forward / backward (bf16; head dims 192/128 or
+ * 128/128).  Replace dense_prefill_fwd / dense_prefill_bwd
+ * (csrc/pybind.cpp:817-867) -> FMHACutlassSM100FwdRun / BwdRun
+ * (csrc/sm100/prefill/dense/fmha_cutlass_{fwd,bwd}_sm100.cu).  Unsupported head
+ * dims return FMLA_ERR_UNSUPPORTED (the reference silently does nothing,
+ * fmha_cutlass_fwd_sm100.cu:110-113).
+ * ------------------------------------------------------------------------- */
+typedef struct fmla_dense_params {
+  int32_t batch;                     /* number of sequences                          */
+  int32_t total_q, total_k;          /* packed token counts                          */
+  int32_t h_q, h_k, d_qk, d_v;
+  int32_t max_seqlen_q, max_seqlen_k;
+  int32_t is_causal;                 /* mask_mode_code: 0 none, 1 causal (bottom-right aligned) */
+  float softmax_scale;
+  const void* q; int64_t q_stride_t, q_stride_h;     /* bf16 [total_q, h_q, d_qk] */
+  const void* k; int64_t k_stride_t, k_stride_h;     /* bf16 [total_k, h_k, d_qk] */
+  const void* v; int64_t v_stride_t, v_stride_h;     /* bf16 [total_k, h_k, d_v]  */
+  const int32_t* cu_seqlens_q;       /* [batch+1] */
+  const int32_t* cu_seqlens_k;       /* [batch+1] */
+  void* o;       int64_t o_stride_t, o_stride_h;     /* bf16 [total_q, h_q, d_v]  */
+  float* lse;    int64_t lse_stride_t, lse_stride_h; /* fp32 [total_q, h_q] natural log, -inf for empty rows */
+  /* backward only */
+  const void* d_o; int64_t do_stride_t, do_stride_h; /* bf16 [total_q, h_q, d_v]  */
+  void* dq;      int64_t dq_stride_t, dq_stride_h;   /* bf16 [total_q, h_q, d_qk] */
+  void* dk;      int64_t dk_stride_t, dk_stride_h;   /* bf16 [total_k, h_k, d_qk] */
+  void* dv;      int64_t dv_stride_t, dv_stride_h;   /* bf16 [total_k, h_k, d_v]  */
+  void* workspace; size_t workspace_bytes;           /* >= fmla_dense_bwd_workspace_bytes() */
+} fmla_dense_params;
+
+int fmla_dense_prefill_fwd(const fmla_dense_params* params_host, void* stream);
+size_t fmla_dense_bwd_workspace_bytes(int total_q, int h_q, int d_qk);
+int fmla_dense_prefill_bwd(const fmla_dense_params* params_host, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * FP8 KV-cache writer: bf16 [num_tokens, 576] rows -> 656-byte records
+ * (README.md:162-170; the reference only has the torch helper
+ * tests/quant.py:3-35).  dst_slots[i] = physical slot of token i, or NULL for
+ * slot i = i.
+ * ------------------------------------------------------------------------- */
+int fmla_quantize_kv_fp8(const void* kv_bf16, int64_t kv_stride_row, int num_tokens,
+                         const int32_t* dst_slots, void* cache_bytes, int64_t cache_stride_slot_bytes,
+                         void* stream);
+
+/* sizeof() of the parameter blocks as compiled into the library, so a foreign
+ * binding (ctypes, cgo, JNI ...) can verify its own struct layout at load time. */
+size_t fmla_sizeof_decode_params(void);
+size_t fmla_sizeof_sparse_prefill_params(void);
+size_t fmla_sizeof_dense_params(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHMLA_B200_H_ */

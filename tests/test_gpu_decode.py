@@ -1,0 +1,131 @@
+"""GPU parity of get_mla_metadata + flash_mla_with_kvcache against the CPU oracle
+(grid modelled on tests/test_flash_mla_decoding.py:293-321 of the reference)."""
+import pytest
+import torch
+
+import gpu_util as U
+from golden_io import load
+from oracle import decode, gen, quant, scheduler
+
+pytestmark = pytest.mark.gpu
+
+
+def _api():
+    import flashmla_windows_linux_sm120_b200 as fm
+    return fm
+
+
+def _run_dense(d: gen.DecodeData, t: gen.DecodeCase):
+    fm = _api()
+    lens = d.cache_seqlens.cuda()
+    md, ns = fm.get_mla_metadata(lens, t.s_q * t.h_q // t.h_kv, t.h_kv)
+    out, lse = fm.flash_mla_with_kvcache(d.q.cuda(), d.blocked_k.cuda(), d.block_table.cuda(), lens, t.dv, md, ns,
+                                         causal=t.is_causal)
+    torch.cuda.synchronize()
+    return out.cpu(), lse.cpu(), md.cpu(), ns.cpu()
+
+
+@pytest.mark.parametrize("b,s_q,s_k,varlen,causal,h_q,h_kv", [
+    (1, 1, 20, False, False, 128, 1),
+    (2, 2, 140, True, True, 128, 1),
+    (6, 4, 140, True, True, 128, 1),
+    (6, 1, 1500, True, False, 128, 1),
+    (2, 2, 4096, True, True, 128, 1),
+    (3, 2, 300, True, True, 16, 1),
+    (3, 4, 300, False, False, 64, 1),
+    (2, 2, 260, True, True, 32, 2),
+    (64, 1, 140, True, False, 128, 1),
+])
+def test_dense_decode(b, s_q, s_k, varlen, causal, h_q, h_kv):
+    t = gen.DecodeCase(b=b, s_q=s_q, s_k=s_k, is_varlen=varlen, is_causal=causal, h_q=h_q, h_kv=h_kv)
+    d = gen.make_decode_case(t)
+    out, lse, md, ns = _run_dense(d, t)
+    ref_out, ref_lse = decode.decode_ref(d.cache_seqlens, d.block_table, d.q, d.blocked_k, t.dv, causal)
+    U.assert_out_lse(out, lse, ref_out, ref_lse)
+    scheduler.check_schedule_invariants(md.tolist(), ns.tolist(), d.cache_seqlens.tolist())
+
+
+def test_dense_decode_zero_length_requests():
+    t = gen.DecodeCase(b=16, s_q=2, s_k=500, is_varlen=True, is_causal=True, zero_seqlen=True)
+    d = gen.make_decode_case(t)
+    assert (d.cache_seqlens == 0).any()
+    out, lse, _, _ = _run_dense(d, t)
+    ref_out, ref_lse = decode.decode_ref(d.cache_seqlens, d.block_table, d.q, d.blocked_k, t.dv, True)
+    U.assert_out_lse(out, lse, ref_out, ref_lse)
+
+
+def test_dense_decode_unit_normal_values():
+    # benchmark value distribution: bf16 N(0,1) q and kv
+    t = gen.DecodeCase(b=4, s_q=1, s_k=1024, h_q=16, unit_normal=True)
+    d = gen.make_decode_case(t)
+    out, lse, _, _ = _run_dense(d, t)
+    ref_out, ref_lse = decode.decode_ref(d.cache_seqlens, d.block_table, d.q, d.blocked_k, t.dv, False)
+    U.assert_out_lse(out, lse, ref_out, ref_lse, out_cos=2e-5)
+
+
+@pytest.mark.parametrize("name", ["decode_dense_causal", "decode_dense_plain", "decode_dense_zero", "decode_fallback_path"])
+def test_dense_decode_golden(name):
+    """CUDA path against outputs stored from the reference's own torch code."""
+    fm = _api()
+    g = load(name)
+    b, s_q, h_q, _ = g["q"].shape
+    lens = g["cache_seqlens"].cuda()
+    md, ns = fm.get_mla_metadata(lens, s_q * h_q, 1)
+    out, lse = fm.flash_mla_with_kvcache(g["q"].cuda(), g["blocked_k"].cuda(), g["block_table"].cuda(), lens, 512, md, ns,
+                                         causal=bool(g.get("is_causal", 0)))
+    U.assert_out_lse(out.cpu(), lse.cpu(), g["out"], g["lse"])
+
+
+def _run_sparse(d: gen.DecodeData, t: gen.DecodeCase, kq):
+    fm = _api()
+    lens = d.cache_seqlens.cuda()
+    md, ns = fm.get_mla_metadata(lens, t.s_q * t.h_q // t.h_kv, t.h_kv, t.h_q, True, t.topk)
+    out, lse = fm.flash_mla_with_kvcache(d.q.cuda(), kq.cuda(), d.block_table.cuda(), lens, t.dv, md, ns,
+                                         is_fp8_kvcache=True, indices=d.indices.cuda())
+    torch.cuda.synchronize()
+    return out.cpu(), lse.cpu()
+
+
+@pytest.mark.parametrize("b,s_q,s_k,topk,h_q,invalid", [
+    (1, 1, 140, 128, 128, False),
+    (2, 2, 4096, 128, 128, False),
+    (6, 4, 4096, 2048, 128, False),
+    (2, 2, 1000, 2048, 128, False),       # fewer tokens than topk: -1 padding
+    (3, 1, 600, 256, 64, False),
+    (4, 2, 4096, 128, 128, True),         # every index invalid
+])
+def test_sparse_fp8_decode(b, s_q, s_k, topk, h_q, invalid):
+    t = gen.DecodeCase(b=b, s_q=s_q, s_k=s_k, is_varlen=True, topk=topk, h_q=h_q, all_indices_invalid=invalid)
+    d = gen.make_decode_case(t)
+    kq = quant.quantize_k_cache(d.blocked_k, t.dv, 128)
+    kd = quant.dequantize_k_cache(kq)
+    out, lse = _run_sparse(d, t, kq)
+    ref_out, ref_lse = decode.decode_ref(d.cache_seqlens, d.block_table, d.q, kd, t.dv, False, d.abs_indices)
+    U.assert_out_lse(out, lse, ref_out, ref_lse)
+
+
+@pytest.mark.parametrize("name", ["decode_sparse_fp8", "decode_sparse_fp8_pad"])
+def test_sparse_fp8_decode_golden(name):
+    fm = _api()
+    g = load(name)
+    b, s_q, h_q, _ = g["q"].shape
+    topk = g["indices"].shape[-1]
+    lens = g["cache_seqlens"].cuda()
+    md, ns = fm.get_mla_metadata(lens, s_q * h_q, 1, h_q, True, topk)
+    out, lse = fm.flash_mla_with_kvcache(g["q"].cuda(), g["blocked_k_quant"].cuda(), g["block_table"].cuda(), lens, 512,
+                                         md, ns, is_fp8_kvcache=True, indices=g["indices"].cuda())
+    U.assert_out_lse(out.cpu(), lse.cpu(), g["out"], g["lse"])
+
+
+def test_argument_errors():
+    fm = _api()
+    t = gen.DecodeCase(b=1, s_q=1, s_k=64, h_q=16)
+    d = gen.make_decode_case(t)
+    lens = d.cache_seqlens.cuda()
+    md, ns = fm.get_mla_metadata(lens, 16, 1)
+    with pytest.raises(RuntimeError):
+        fm.flash_mla_with_kvcache(d.q.cuda()[..., :512].contiguous(), d.blocked_k.cuda(), d.block_table.cuda(), lens, 512, md, ns)
+    with pytest.raises(RuntimeError):
+        fm.flash_mla_with_kvcache(d.q.cuda(), d.blocked_k.cuda(), d.block_table.cuda().long(), lens, 512, md, ns)
+    with pytest.raises(RuntimeError):
+        fm.flash_mla_with_kvcache(d.q.cuda().half(), d.blocked_k.cuda().half(), d.block_table.cuda(), lens, 512, md, ns)

@@ -1,0 +1,96 @@
+"""GPU parity of flash_attn_varlen_func forward + backward
+(grid modelled on tests/test_fmha_sm100.py:187-197, scaled down so the fp32 CPU oracle runs in seconds)."""
+import pytest
+import torch
+
+from golden_io import load
+from oracle import dense, gen
+from oracle.check import check_is_allclose
+
+pytestmark = pytest.mark.gpu
+
+# tests/test_fmha_sm100.py:126-133
+TOL = dict(abs_tol=1e-3, rel_tol=8.01 / 128, cos_diff_tol=7e-6)
+LSE_TOL = dict(abs_tol=1e-6, rel_tol=2.01 / 65536)
+
+
+def _run(c, causal, bwd):
+    import flashmla_windows_linux_sm120_b200 as fm
+    q, k, v = (c[n].cuda().requires_grad_(bwd) for n in ("q", "k", "v"))
+    out, lse = fm.flash_attn_varlen_func(q, k, v, c["cu_q"].cuda(), c["cu_k"].cuda(), c["max_q"], c["max_k"],
+                                         softmax_scale=c["scale"], causal=causal)
+    grads = None
+    if bwd:
+        out.backward(c["d_out"].cuda())
+        grads = (q.grad.cpu(), k.grad.cpu(), v.grad.cpu())
+    torch.cuda.synchronize()
+    return out.detach().cpu(), lse.detach().cpu(), grads
+
+
+@pytest.mark.parametrize("d,dv", [(192, 128), (128, 128)])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("varlen", [False, True])
+def test_dense_fwd_bwd(d, dv, causal, varlen):
+    c = gen.make_dense_case(gen.DenseCase(b=3, mean_sq=200, mean_sk=200, varlen=varlen, h=4, h_k=4, d=d, dv=dv,
+                                          causal=causal))
+    out, lse, (dq, dk, dvv) = _run(c, causal, True)
+    r_out, r_lse, r_dq, r_dk, r_dv = dense.dense_fwd_bwd_ref(c["q"], c["k"], c["v"], c["d_out"], c["cu_q"], c["cu_k"],
+                                                             causal, c["scale"])
+    assert check_is_allclose("out", out, r_out, **TOL)
+    assert check_is_allclose("lse", lse, r_lse, **LSE_TOL)
+    assert check_is_allclose("dq", dq, r_dq, **TOL)
+    assert check_is_allclose("dk", dk, r_dk, **TOL)
+    assert check_is_allclose("dv", dvv, r_dv, **TOL)
+
+
+@pytest.mark.parametrize("d", [192, 128])
+def test_dense_fwd_gqa(d):
+    c = gen.make_dense_case(gen.DenseCase(b=2, mean_sq=150, mean_sk=260, varlen=True, h=8, h_k=2, d=d, dv=128, causal=True))
+    out, lse, _ = _run(c, True, False)
+    r_out, r_lse = dense.dense_fwd_ref(c["q"], c["k"], c["v"], c["cu_q"], c["cu_k"], True, c["scale"])
+    assert check_is_allclose("out", out, r_out, **TOL)
+    assert check_is_allclose("lse", lse, r_lse, **LSE_TOL)
+
+
+def test_dense_bitwise_determinism():
+    c = gen.make_dense_case(gen.DenseCase(b=2, mean_sq=300, mean_sk=300, varlen=True, h=4, h_k=4, d=192, dv=128, causal=True))
+    first = _run(c, True, True)
+    for _ in range(3):
+        again = _run(c, True, True)
+        assert torch.equal(first[0], again[0]) and torch.equal(first[1], again[1])
+        for a, b in zip(first[2], again[2]):     # dq too: every output has a single, ordered producer
+            assert torch.equal(a, b)
+
+
+def test_dense_bwd_rejects_gqa():
+    c = gen.make_dense_case(gen.DenseCase(b=1, mean_sq=64, mean_sk=64, varlen=False, h=4, h_k=2, d=128, dv=128, causal=False))
+    with pytest.raises(ValueError):
+        _run(c, False, True)
+
+
+def test_dense_rejects_unsupported_head_dim():
+    import flashmla_windows_linux_sm120_b200 as fm
+    q = torch.zeros(64, 2, 64, dtype=torch.bfloat16, device="cuda")
+    cu = torch.tensor([0, 64], dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError):
+        fm.flash_attn_varlen_func(q, q, q, cu, cu, 64, 64)
+
+
+@pytest.mark.parametrize("name", ["dense_mla192_causal", "dense_128_plain_gqa"])
+def test_dense_golden(name):
+    import flashmla_windows_linux_sm120_b200 as fm
+    g = load(name)
+    causal = bool(g["causal"])
+    bwd = "dq" in g
+    q, k, v = (g[n].cuda().requires_grad_(bwd) for n in ("q", "k", "v"))
+    cu_q, cu_k = g["cu_q"], g["cu_k"]
+    mq = int((cu_q[1:] - cu_q[:-1]).max())
+    mk = int((cu_k[1:] - cu_k[:-1]).max())
+    out, lse = fm.flash_attn_varlen_func(q, k, v, cu_q.cuda(), cu_k.cuda(), mq, mk, softmax_scale=g["scale"], causal=causal)
+    assert check_is_allclose("out", out.detach(), g["out"], **TOL)
+    assert check_is_allclose("lse", lse.detach(), g["lse"], **LSE_TOL)
+    if bwd:
+        out.backward(g["d_out"].cuda())
+        assert check_is_allclose("dq", q.grad, g["dq"], **TOL)
+        assert check_is_allclose("dk", k.grad, g["dk"], **TOL)
+        assert check_is_allclose("dv", v.grad, g["dv"], **TOL)
