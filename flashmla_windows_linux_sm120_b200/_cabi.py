@@ -77,6 +77,7 @@ SYMBOLS = {
     "fmla_dense_bwd_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "fmla_dense_prefill_bwd": (C.c_int, [C.POINTER(DenseParams), vp]),
     "fmla_quantize_kv_fp8": (C.c_int, [vp, i64, C.c_int, vp, vp, i64, vp]),
+    "fmla_device_status": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
     "fmla_sizeof_decode_params": (C.c_size_t, []),
     "fmla_sizeof_sparse_prefill_params": (C.c_size_t, []),
     "fmla_sizeof_dense_params": (C.c_size_t, []),

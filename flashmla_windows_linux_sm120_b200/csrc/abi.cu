@@ -8,6 +8,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 namespace {
@@ -186,7 +187,12 @@ int fmla_fwd_kvcache_mla(const fmla_decode_params* P, void* stream) {
     e = cudaEventRecord(static_cast<cudaEvent_t>(a.profile_event_begin), s);
     if (e != cudaSuccess) return cuda_fail(e, "cudaEventRecord");
   }
-  e = fmla::launch_decode_mma(k, s);
+  if (sparse) {
+    e = fmla::launch_decode_mma(k, s);
+  } else {
+    static const bool use_mma = [] { const char* v = getenv("FMLA_DENSE_DECODE_MMA"); return v && v[0] == '1'; }();
+    e = use_mma ? fmla::launch_decode_mma(k, s) : fmla::launch_decode_dense_tc(k, s);
+  }
   if (e != cudaSuccess) return cuda_fail(e, "decode attention launch");
   if (a.profile_event_end) {
     e = cudaEventRecord(static_cast<cudaEvent_t>(a.profile_event_end), s);
@@ -300,6 +306,13 @@ int fmla_dense_prefill_bwd(const fmla_dense_params* P, void* stream) {
   if (rc) return rc;
   cudaError_t e = fmla::launch_dense_bwd_mma(k, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? FMLA_OK : cuda_fail(e, "dense backward launch");
+}
+
+int fmla_device_status(int* status_host, int reset) {
+  FMLA_REQUIRE(status_host != nullptr, "status_host is null");
+  cudaError_t e = fmla::read_decode_tc_status(status_host, reset != 0);
+  if (e != cudaSuccess) return cuda_fail(e, "reading the device status word");
+  return *status_host == 0 ? FMLA_OK : fail(FMLA_ERR_DEVICE_TIMEOUT, "a bounded device-side wait expired (code %d)", *status_host);
 }
 
 int fmla_quantize_kv_fp8(const void* kv_bf16, int64_t kv_stride_row, int num_tokens, const int32_t* dst_slots,

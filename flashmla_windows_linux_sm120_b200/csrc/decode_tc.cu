@@ -1,0 +1,449 @@
+// Dense BF16 split-KV MLA decode for sm_100a: TMA -> 128B-swizzled shared
+// memory -> tcgen05.mma (weight-stationary M=64 form) with S and O in tensor
+// memory, warp-specialised online softmax.
+//
+// One CTA = one query token's 64-head tile for one schedule partition.
+//   warp 4   producer : TMA loads of the Q tile (9 boxes of 64 rows x 64 cols) and of
+//                       one 64-token cache page per step (9 boxes), 2-stage ring
+//   warp 5   MMA      : S = Q K^T  (36 x tcgen05.mma.ws m64n64k16)  -> TMEM S[stage]
+//                       O += P V   ( 8 x tcgen05.mma.ws m64n256k16) -> TMEM O
+//                       V is the first 512 columns of the same K tile, read MN-major
+//   warps 0-3 softmax : TMEM S -> registers, mask, running max / sum (base 2),
+//                       P (bf16) -> shared memory, lazy rescale of O in TMEM,
+//                       final 1/l normalisation and the store of O / LSE
+// TMEM map (512 columns allocated): O = [0,256) (two N=256 halves of 128 columns),
+// S[0] = [256,288), S[1] = [288,320).  In the M=64 weight-stationary layout element
+// (row r, col c) of an N-wide result sits in lane r + 64*(c >= N/2), column c % (N/2).
+//
+// Semantics (borders, split / no-split outputs, LSE conventions) are those of the
+// reference decode kernels: csrc/sm90/decode/dense/splitkv_mla.cu:948-957, 1022-1042,
+// 1237-1269.  Every mbarrier wait is bounded (tc_common.cuh); a pipeline fault sets
+// a status word and lets the CTA drain and free its tensor memory.
+#include "kernels.h"
+#include "tc_common.cuh"
+
+#include <cuda.h>
+
+namespace fmla {
+
+namespace dtc {
+constexpr int kChunkBytes = 64 * 128;             // [64 rows x 64 bf16], 128-byte rows
+constexpr int kTileBytes = 9 * kChunkBytes;       // 64 x 576 bf16
+constexpr int Q_OFF = 0;
+constexpr int KV_OFF = kTileBytes;                // 2 stages
+constexpr int P_OFF = 3 * kTileBytes;             // [64 x 64] bf16
+constexpr int BAR_OFF = P_OFF + kChunkBytes;      // mbarriers
+constexpr int MX_OFF = BAR_OFF + 128;             // float [3][128] exchange (2 for row maxima, 1 for row sums)
+constexpr int MISC_OFF = MX_OFF + 1536;           // tmem base, abort flag
+constexpr int SMEM_BYTES = MISC_OFF + 64 + 1024;  // + slack for manual 1024-byte alignment
+enum Bar { Q_FULL = 0, Q_EMPTY, KV_FULL0, KV_FULL1, KV_EMPTY0, KV_EMPTY1, S_FULL0, S_FULL1, S_EMPTY0, S_EMPTY1, P_FULL, P_EMPTY, O_FULL, O_EMPTY, NUM_BARS };
+constexpr int TMEM_O = 0, TMEM_S = 256;
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory limit per CTA");
+static_assert(NUM_BARS * 8 <= 128, "barrier area too small");
+constexpr float kRescaleThreshold = 8.0f;         // log2 units; below it O keeps its stale scale
+}  // namespace dtc
+
+__device__ int g_decode_tc_status = 0;
+
+struct ReqInfo {
+  int blk_lo, blk_hi, seqlen, border, split_slot;
+  bool no_split;
+};
+
+__device__ __forceinline__ ReqInfo request_info(const DecodeKernelParams& p, int batch, int sq, int begin_idx, int end_idx,
+                                                int begin_block, int end_block, int begin_split) {
+  ReqInfo r;
+  r.seqlen = __ldg(p.seqlens_k + batch);
+  const int nblk_total = (r.seqlen + 63) >> 6;
+  r.border = p.is_causal ? r.seqlen - (p.s_q - 1 - sq) : r.seqlen;
+  const int nblk_visible = r.border > 0 ? (r.border + 63) >> 6 : 0;
+  r.blk_lo = batch == begin_idx ? begin_block : 0;
+  r.blk_hi = min(min(batch == end_idx ? end_block : nblk_total, nblk_total), nblk_visible);
+  if (r.blk_hi < r.blk_lo) r.blk_hi = r.blk_lo;
+  const int lo = __ldg(p.num_splits + batch);
+  r.no_split = __ldg(p.num_splits + batch + 1) - lo == 1;
+  r.split_slot = lo + (batch == begin_idx ? begin_split : 0);
+  return r;
+}
+
+// grid (s_q * ceil(hq_per_hk/64), h_k, num_sm_parts), 192 threads
+__global__ void __launch_bounds__(192, 1)
+decode_dense_tc_kernel(const __grid_constant__ DecodeKernelParams p, const __grid_constant__ CUtensorMap tmap_q,
+                       const __grid_constant__ CUtensorMap tmap_kv) {
+  using namespace dtc;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t sQ = sbase + Q_OFF, sKV = sbase + KV_OFF, sP = sbase + P_OFF;
+  auto bar = [&](int i) { return sbase + BAR_OFF + i * 8; };
+  float* sMx = reinterpret_cast<float*>(smem + MX_OFF);
+  volatile uint32_t* sTmem = reinterpret_cast<volatile uint32_t*>(smem + MISC_OFF);
+  volatile int* sAbort = reinterpret_cast<volatile int*>(smem + MISC_OFF + 8);   // set by a softmax thread whose wait expired
+  int* status = &g_decode_tc_status;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_hb = (p.hq_per_hk + 63) >> 6;
+  const int sq = blockIdx.x / n_hb, hb = blockIdx.x % n_hb;
+  const int kh = blockIdx.y, part = blockIdx.z;
+  const int head0 = kh * p.hq_per_hk + hb * 64;                 // first q head of the tile
+  const int nvalid = min(64, p.hq_per_hk - hb * 64);
+
+  const int4 md = __ldg(reinterpret_cast<const int4*>(p.tile_scheduler_metadata + part * 8));
+  const int begin_idx = md.x, begin_block = md.y, end_idx = md.z, end_block = md.w;
+  const int begin_split = __ldg(p.tile_scheduler_metadata + part * 8 + 4);
+  if (begin_idx >= p.b) return;
+
+  if (tid == 0) {
+    tc::mbar_init(bar(Q_FULL), 1);
+    tc::mbar_init(bar(Q_EMPTY), 1);
+    tc::mbar_init(bar(KV_FULL0), 1);
+    tc::mbar_init(bar(KV_FULL1), 1);
+    tc::mbar_init(bar(KV_EMPTY0), 1);
+    tc::mbar_init(bar(KV_EMPTY1), 1);
+    tc::mbar_init(bar(S_FULL0), 1);
+    tc::mbar_init(bar(S_FULL1), 1);
+    tc::mbar_init(bar(S_EMPTY0), 128);
+    tc::mbar_init(bar(S_EMPTY1), 128);
+    tc::mbar_init(bar(P_FULL), 128);
+    tc::mbar_init(bar(P_EMPTY), 1);
+    tc::mbar_init(bar(O_FULL), 1);
+    tc::mbar_init(bar(O_EMPTY), 128);
+    tc::fence_mbar_init();
+    *sAbort = 0;
+  }
+  if (warp == 5) tc::tmem_alloc(sbase + MISC_OFF, 512);
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = *sTmem;
+
+  if (warp == 4) {
+    // ================================ producer =========================================
+    if (lane == 0) {
+      tc::prefetch_tensormap(&tmap_q);
+      tc::prefetch_tensormap(&tmap_kv);
+      int g = 0, req = 0;
+      bool alive = true;
+      for (int batch = begin_idx; batch <= end_idx && alive; ++batch) {
+        const ReqInfo r = request_info(p, batch, sq, begin_idx, end_idx, begin_block, end_block, begin_split);
+        if (r.blk_hi == r.blk_lo) continue;
+        alive = tc::mbar_wait(bar(Q_EMPTY), (req & 1) ^ 1, status, 1);
+        if (!alive) break;
+        tc::mbar_arrive_expect_tx(bar(Q_FULL), kTileBytes);
+#pragma unroll
+        for (int c = 0; c < 9; ++c) tc::tma_load_4d(sQ + c * kChunkBytes, &tmap_q, c * 64, head0, sq, batch, bar(Q_FULL));
+        const int* bt = p.block_table + batch * p.block_table_stride_b;
+        int page_next = __ldg(bt + r.blk_lo);
+        for (int blk = r.blk_lo; blk < r.blk_hi; ++blk, ++g) {
+          const int st = g & 1;
+          const int page = page_next;
+          if (blk + 1 < r.blk_hi) page_next = __ldg(bt + blk + 1);
+          alive = tc::mbar_wait(bar(KV_EMPTY0 + st), ((g >> 1) & 1) ^ 1, status, 2);
+          if (!alive) break;
+          tc::mbar_arrive_expect_tx(bar(KV_FULL0 + st), kTileBytes);
+#pragma unroll
+          for (int c = 0; c < 9; ++c)
+            tc::tma_load_4d(sKV + st * kTileBytes + c * kChunkBytes, &tmap_kv, c * 64, kh, 0, page, bar(KV_FULL0 + st));
+        }
+        ++req;
+      }
+    }
+  } else if (warp == 5) {
+    // ================================ MMA issuer =======================================
+    constexpr uint32_t idesc_s = tc::idesc_bf16_f32(64, 64, 0, 0);
+    constexpr uint32_t idesc_o = tc::idesc_bf16_f32(64, 256, 0, 1);
+    int g = 0, req = 0;
+    bool alive = true;
+    auto issue_pv = [&](int gi, bool first_of_request, int req_idx) {
+      const int st = gi & 1;
+      alive = alive && tc::mbar_wait(bar(P_FULL), gi & 1, status, 3);
+      if (first_of_request) alive = alive && tc::mbar_wait(bar(O_EMPTY), (req_idx & 1) ^ 1, status, 4);
+      alive = __all_sync(0xffffffffu, alive);
+      if (!alive) return;
+      tc::tc_fence_after();
+      if (lane == 0) {
+        const uint32_t v_base = sKV + st * kTileBytes;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int s = 0; s < 4; ++s) {
+            const uint64_t da = tc::smem_desc_sw128(sP + s * 32, 16, 1024);
+            const uint64_t db = tc::smem_desc_sw128(v_base + h * 4 * kChunkBytes + s * 2048, kChunkBytes, 1024);
+            tc::mma_ws_ss(tmem + TMEM_O + h * 128, da, db, idesc_o, (first_of_request && s == 0) ? 0u : 1u);
+          }
+        tc::tc_commit(bar(KV_EMPTY0 + st));
+        tc::tc_commit(bar(P_EMPTY));
+      }
+      __syncwarp();
+    };
+    for (int batch = begin_idx; batch <= end_idx && alive; ++batch) {
+      const ReqInfo r = request_info(p, batch, sq, begin_idx, end_idx, begin_block, end_block, begin_split);
+      const int nblk = r.blk_hi - r.blk_lo;
+      if (nblk == 0) continue;
+      alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_FULL), req & 1, status, 5));
+      const int g0 = g;
+      for (int j = 0; j < nblk && alive; ++j, ++g) {
+        const int st = g & 1;
+        alive = tc::mbar_wait(bar(KV_FULL0 + st), (g >> 1) & 1, status, 6);
+        alive = alive && tc::mbar_wait(bar(S_EMPTY0 + st), ((g >> 1) & 1) ^ 1, status, 7);
+        alive = __all_sync(0xffffffffu, alive);
+        if (!alive) break;
+        // rows of the last page beyond the sequence may hold anything (NaN included): zero them so
+        // that 0 * garbage cannot reach O through P V
+        const int rows_valid = r.seqlen - (r.blk_lo + j) * 64;
+        if (rows_valid < 64) {
+          unsigned char* stage = smem + KV_OFF + st * kTileBytes;
+          const int nrows = 64 - rows_valid;
+          for (int i = lane; i < nrows * 72; i += 32) {
+            const int row = rows_valid + i / 72, c16 = i % 72;
+            *reinterpret_cast<uint4*>(stage + (c16 >> 3) * kChunkBytes + row * 128 + (c16 & 7) * 16) = make_uint4(0, 0, 0, 0);
+          }
+          tc::fence_proxy_async_smem();
+          __syncwarp();
+        }
+        tc::tc_fence_after();
+        if (lane == 0) {
+          const uint32_t k_base = sKV + st * kTileBytes;
+#pragma unroll
+          for (int c = 0; c < 9; ++c)
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+              const uint64_t da = tc::smem_desc_sw128(sQ + c * kChunkBytes + s * 32, 16, 1024);
+              const uint64_t db = tc::smem_desc_sw128(k_base + c * kChunkBytes + s * 32, 16, 1024);
+              tc::mma_ws_ss(tmem + TMEM_S + st * 32, da, db, idesc_s, (c | s) ? 1u : 0u);
+            }
+          tc::tc_commit(bar(S_FULL0 + st));
+          if (j == nblk - 1) tc::tc_commit(bar(Q_EMPTY));
+        }
+        __syncwarp();
+        if (j >= 1) issue_pv(g - 1, j == 1, req);
+      }
+      if (alive) issue_pv(g0 + nblk - 1, nblk == 1, req);
+      if (alive && lane == 0) tc::tc_commit(bar(O_FULL));
+      __syncwarp();
+      ++req;
+    }
+  } else {
+    // ================================ softmax / epilogue ================================
+    const int r_row = tid & 63, th = tid >> 6;           // TMEM lane tid: row tid%64, token/column half tid/64
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const int q_seq_per_hk = p.s_q * p.hq_per_hk;
+    int g = 0, req = 0;
+    bool aborted = false;        // uniform over the 128 softmax threads: only read right after a bar_sync
+    for (int batch = begin_idx; batch <= end_idx; ++batch) {
+      const ReqInfo r = request_info(p, batch, sq, begin_idx, end_idx, begin_block, end_block, begin_split);
+      const int nblk = r.blk_hi - r.blk_lo;
+      float m_run = neg_inf();     // running maximum (base-2 scaled logits)
+      float m_used = 0.f;          // the maximum O and l are currently scaled with
+      float l_part = 0.f;          // this thread's share of the row sum
+      for (int j = 0; j < nblk && !aborted; ++j, ++g) {
+        const int st = g & 1;
+        uint32_t sv[32];
+        if (tc::mbar_wait(bar(S_FULL0 + st), (g >> 1) & 1, status, 8)) {
+          tc::tc_fence_after();
+          tc::tmem_ld32(tmem + lane_addr + TMEM_S + st * 32, sv);
+          tc::tmem_wait_ld();
+          tc::tc_fence_before();
+        } else {
+          *sAbort = 1;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sv[i] = 0u;
+        }
+        tc::mbar_arrive(bar(S_EMPTY0 + st));
+
+        const int tok0 = (r.blk_lo + j) * 64 + th * 32;
+        float s[32];
+        float mx = neg_inf();
+        if (tok0 + 32 > r.border) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            s[i] = (tok0 + i < r.border) ? __uint_as_float(sv[i]) * p.scale_log2 : neg_inf();
+            mx = fmaxf(mx, s[i]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            s[i] = __uint_as_float(sv[i]) * p.scale_log2;
+            mx = fmaxf(mx, s[i]);
+          }
+        }
+        float* xch = sMx + (j & 1) * 128;
+        xch[tid] = mx;
+        bar_sync(1, 128);
+        if (*sAbort) { aborted = true; break; }
+        mx = fmaxf(mx, xch[tid ^ 64]);
+        const float m_new = fmaxf(m_run, mx);
+
+        // O and l carry the scale 2^-m_used; it is moved only when the maximum grew by more than the
+        // threshold (or when the first real value arrives after fully masked blocks)
+        bool need = false;
+        if (j == 0) {
+          m_used = (m_new == neg_inf()) ? 0.f : m_new;
+        } else {
+          need = (m_new - m_used) > kRescaleThreshold || (m_run == neg_inf() && m_new != neg_inf());
+        }
+        m_run = m_new;
+        // the previous P V must be complete before P is overwritten and before O may be rescaled
+        if (!tc::mbar_wait(bar(P_EMPTY), (g & 1) ^ 1, status, 9)) *sAbort = 1;
+        if (__any_sync(0xffffffffu, need)) {
+          const float m_next = need ? m_new : m_used;
+          const float alpha = exp2f(m_used - m_next);
+          m_used = m_next;
+          l_part *= alpha;
+          tc::tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            uint32_t ov[32];
+            tc::tmem_ld32(tmem + lane_addr + TMEM_O + c * 32, ov);
+            tc::tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tc::tmem_st32(tmem + lane_addr + TMEM_O + c * 32, ov);
+          }
+          tc::tmem_wait_st();
+          tc::tc_fence_before();
+        }
+        float rs = 0.f;
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = exp2f(s[2 * i] - m_used), p1 = exp2f(s[2 * i + 1] - m_used);
+          rs += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        l_part += rs;
+        // P[row][th*32 .. +32) -> K-major 128B-swizzled A operand: 16-byte chunk (th*4 + q) ^ (row & 7)
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const uint32_t dst = sP + r_row * 128 + ((((th * 4 + q4) ^ (r_row & 7))) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(dst), "r"(pk[q4 * 4]), "r"(pk[q4 * 4 + 1]), "r"(pk[q4 * 4 + 2]), "r"(pk[q4 * 4 + 3]) : "memory");
+        }
+        tc::fence_proxy_async_smem();
+        tc::mbar_arrive(bar(P_FULL));
+      }
+
+      // ---- epilogue of this request --------------------------------------------------
+      float* xch = sMx + 256;
+      bar_sync(1, 128);
+      xch[tid] = l_part;
+      bar_sync(1, 128);
+      if (*sAbort) aborted = true;
+      if (aborted) break;
+      const float l = l_part + xch[tid ^ 64];
+      const bool row_ok = r_row < nvalid;
+      const int head = head0 + r_row;
+      const float inv = (l == 0.f || nblk == 0) ? 0.f : 1.f / l;
+      bool have_o = nblk > 0;
+      if (have_o) {
+        if (!tc::mbar_wait(bar(O_FULL), req & 1, status, 10)) { *sAbort = 1; have_o = false; }
+        tc::tc_fence_after();
+      }
+      const int row_in_group = sq * p.hq_per_hk + hb * 64 + r_row;   // regrouped row index within the kv head
+      __nv_bfloat16* o_final = reinterpret_cast<__nv_bfloat16*>(p.out) + batch * p.o_stride_b + sq * p.o_stride_s + head * p.o_stride_h;
+      float* o_part = p.o_accum + (((int64_t)r.split_slot * p.h_k + kh) * q_seq_per_hk + row_in_group) * 512;
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t ov[32];
+        if (have_o) {
+          tc::tmem_ld32(tmem + lane_addr + TMEM_O + c * 32, ov);
+          tc::tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = 0u;
+        }
+        const int col = (c >> 2) * 256 + th * 128 + (c & 3) * 32;
+        if (row_ok) {
+          if (r.no_split) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(ov[q4 * 8 + 0]) * inv, __uint_as_float(ov[q4 * 8 + 1]) * inv);
+              v.y = pack_bf16x2(__uint_as_float(ov[q4 * 8 + 2]) * inv, __uint_as_float(ov[q4 * 8 + 3]) * inv);
+              v.z = pack_bf16x2(__uint_as_float(ov[q4 * 8 + 4]) * inv, __uint_as_float(ov[q4 * 8 + 5]) * inv);
+              v.w = pack_bf16x2(__uint_as_float(ov[q4 * 8 + 6]) * inv, __uint_as_float(ov[q4 * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(o_final + col + q4 * 8) = v;
+            }
+          } else {
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4) {
+              float4 v = make_float4(__uint_as_float(ov[q4 * 4 + 0]) * inv, __uint_as_float(ov[q4 * 4 + 1]) * inv,
+                                     __uint_as_float(ov[q4 * 4 + 2]) * inv, __uint_as_float(ov[q4 * 4 + 3]) * inv);
+              *reinterpret_cast<float4*>(o_part + col + q4 * 4) = v;
+            }
+          }
+        }
+      }
+      if (nblk > 0) {
+        tc::tc_fence_before();
+        tc::mbar_arrive(bar(O_EMPTY));
+        ++req;
+      }
+      if (row_ok && th == 0) {
+        if (r.no_split)
+          p.softmax_lse[((int64_t)batch * p.h_q + head) * p.s_q + sq] = inv == 0.f ? pos_inf() : (log2f(l) + m_used) * kLn2;
+        else
+          p.lse_accum[((int64_t)r.split_slot * p.h_k + kh) * q_seq_per_hk + row_in_group] = inv == 0.f ? neg_inf() : log2f(l) + m_used;
+      }
+    }
+  }
+
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tc::tmem_dealloc(tmem, 512);
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess) f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+// bf16 tensor [d3][d2][d1][d0=576] with element strides s1,s2,s3 ; box {64, b1, b2, 1}
+static bool make_map_4d(CUtensorMap* m, const void* base, uint64_t d1, uint64_t d2, uint64_t d3, int64_t s1, int64_t s2, int64_t s3,
+                        uint32_t b1, uint32_t b2) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[4] = {576, d1, d2, d3};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(s1) * 2, static_cast<cuuint64_t>(s2) * 2, static_cast<cuuint64_t>(s3) * 2};
+  cuuint32_t box[4] = {64, b1, b2, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+cudaError_t launch_decode_dense_tc(const DecodeKernelParams& p, cudaStream_t stream) {
+  CUtensorMap tq, tkv;
+  // q [b][s_q][h_q][576] ; box = 64 heads x 64 columns (heads past h_q read as zero)
+  if (!make_map_4d(&tq, p.q, p.h_q, p.s_q, p.b, p.q_stride_h, p.q_stride_s, p.q_stride_b, 64, 1)) return cudaErrorInvalidValue;
+  // cache [num_blocks][64][h_k][576] addressed as (col, head, row-in-page, page) ; box = 64 rows x 64 columns of one head
+  if (!make_map_4d(&tkv, p.kcache, p.h_k, 64, p.num_blocks, p.k_stride_head, p.k_stride_row, p.k_stride_block, 1, 64))
+    return cudaErrorInvalidValue;
+  auto kern = decode_dense_tc_kernel;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dtc::SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  const int n_hb = (p.hq_per_hk + 63) / 64;
+  dim3 grid(p.s_q * n_hb, p.h_k, p.num_sm_parts);
+  kern<<<grid, 192, dtc::SMEM_BYTES, stream>>>(p, tq, tkv);
+  return cudaGetLastError();
+}
+
+cudaError_t read_decode_tc_status(int* host_status, bool reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(host_status, g_decode_tc_status, sizeof(int));
+  if (e != cudaSuccess) return e;
+  if (reset && *host_status != 0) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_decode_tc_status, &zero, sizeof(int));
+  }
+  return e;
+}
+
+}  // namespace fmla

@@ -69,6 +69,10 @@ struct DenseKernelParams {
 cudaError_t launch_get_mla_metadata(const int* seqlens_k, int batch, int num_sm_parts, int topk, int* md,
                                     int* num_splits, cudaStream_t stream);
 cudaError_t launch_decode_mma(const DecodeKernelParams& p, cudaStream_t stream);
+// dense BF16 decode on tcgen05 / TMA (decode_tc.cu)
+cudaError_t launch_decode_dense_tc(const DecodeKernelParams& p, cudaStream_t stream);
+// reads (and optionally clears) the status word the tcgen05 kernels set when a bounded wait expires
+cudaError_t read_decode_tc_status(int* host_status, bool reset);
 // Merge of split partials for a decode call (reads num_splits; skips unsplit requests).
 cudaError_t launch_decode_combine(const DecodeKernelParams& p, cudaStream_t stream);
 // Stand-alone merge of num_parts partial slots for `rows` rows.

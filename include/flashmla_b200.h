@@ -204,6 +204,13 @@ int fmla_quantize_kv_fp8(const void* kv_bf16, int64_t kv_stride_row, int num_tok
                          const int32_t* dst_slots, void* cache_bytes, int64_t cache_stride_slot_bytes,
                          void* stream);
 
+/* Synchronises the current device and reads the status word that the tcgen05
+ * kernels set when one of their bounded waits (mbarrier polls) gives up instead
+ * of hanging: 0 = no fault.  Returns FMLA_ERR_DEVICE_TIMEOUT when it is non-zero;
+ * `reset` != 0 clears it.  The reference has no counterpart: its kernels wait
+ * without bound and trap on failed asserts (csrc/utils.h:24-30). */
+int fmla_device_status(int* status_host, int reset);
+
 /* sizeof() of the parameter blocks as compiled into the library, so a foreign
  * binding (ctypes, cgo, JNI ...) can verify its own struct layout at load time. */
 size_t fmla_sizeof_decode_params(void);
