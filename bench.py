@@ -105,7 +105,7 @@ class DenseDecode:
     """BASELINE config 2: dense BF16 MLA decode at the DeepSeek-V3 shape."""
     metric, unit, dtype = "dense_bf16_mla_decode_bandwidth", "GB/s", "bf16"
     bound = "hbm"
-    kernel_name = "decode_splitkv_kernel<dense>"
+    kernel_name = "decode_dense_tc_kernel"
     launches_per_step = 2          # split-KV attention + combine
 
     def __init__(self, s_q: int = 1, batch: int = 128, h_q: int = 128):

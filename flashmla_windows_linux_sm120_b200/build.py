@@ -54,7 +54,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     def compile_one(job):
         src, obj = job
-        cmd = [nvcc] + NVCC_FLAGS + ["-I", INCLUDE_DIR, "-c", src, "-o", obj]
+        extra = os.environ.get("FMLA_EXTRA_NVCC_FLAGS", "").split()     # e.g. -DFMLA_TRACE for a timeline build
+        cmd = [nvcc] + NVCC_FLAGS + extra + ["-I", INCLUDE_DIR, "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         r = subprocess.run(cmd, capture_output=True, text=True)

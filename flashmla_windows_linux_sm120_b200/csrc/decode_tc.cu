@@ -40,10 +40,22 @@ enum Bar { Q_FULL = 0, Q_EMPTY, KV_FULL0, KV_FULL1, KV_EMPTY0, KV_EMPTY1, S_FULL
 constexpr int TMEM_O = 0, TMEM_S = 256;
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory limit per CTA");
 static_assert(NUM_BARS * 8 <= 128, "barrier area too small");
+constexpr int kPrefetchDist = 6;                  // cache pages prefetched into L2 ahead of the stage loads
 constexpr float kRescaleThreshold = 8.0f;         // log2 units; below it O keeps its stale scale
 }  // namespace dtc
 
 __device__ int g_decode_tc_status = 0;
+
+// Optional timeline of the first blocks of CTA (0,0,0), compiled in with -DFMLA_TRACE only.
+#ifdef FMLA_TRACE
+__device__ long long g_decode_trace[64 * 16];
+#define FMLA_TRACE_AT(blk, slot)                                                          \
+  do {                                                                                     \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (blk) < 64) g_decode_trace[(blk) * 16 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define FMLA_TRACE_AT(blk, slot) do {} while (0)
+#endif
 
 struct ReqInfo {
   int blk_lo, blk_hi, seqlen, border, split_slot;
@@ -119,7 +131,7 @@ decode_dense_tc_kernel(const __grid_constant__ DecodeKernelParams p, const __gri
 
   if (warp == 4) {
     // ================================ producer =========================================
-    if (lane == 0) {
+    if (tc::elect_one()) {
       tc::prefetch_tensormap(&tmap_q);
       tc::prefetch_tensormap(&tmap_kv);
       int g = 0, req = 0;
@@ -133,13 +145,26 @@ decode_dense_tc_kernel(const __grid_constant__ DecodeKernelParams p, const __gri
 #pragma unroll
         for (int c = 0; c < 9; ++c) tc::tma_load_4d(sQ + c * kChunkBytes, &tmap_q, c * 64, head0, sq, batch, bar(Q_FULL));
         const int* bt = p.block_table + batch * p.block_table_stride_b;
+        // pages kPrefetchDist steps ahead are pulled into L2 while the two shared-memory stages are
+        // busy, so that the load that later fills a stage sees L2 latency instead of HBM latency
+        for (int blk = r.blk_lo; blk < min(r.blk_lo + kPrefetchDist, r.blk_hi); ++blk) {
+          const int pg = __ldg(bt + blk);
+#pragma unroll
+          for (int c = 0; c < 9; ++c) tc::tma_prefetch_l2_4d(&tmap_kv, c * 64, kh, 0, pg);
+        }
         int page_next = __ldg(bt + r.blk_lo);
         for (int blk = r.blk_lo; blk < r.blk_hi; ++blk, ++g) {
           const int st = g & 1;
           const int page = page_next;
           if (blk + 1 < r.blk_hi) page_next = __ldg(bt + blk + 1);
+          if (blk + kPrefetchDist < r.blk_hi) {
+            const int pg = __ldg(bt + blk + kPrefetchDist);
+#pragma unroll
+            for (int c = 0; c < 9; ++c) tc::tma_prefetch_l2_4d(&tmap_kv, c * 64, kh, 0, pg);
+          }
           alive = tc::mbar_wait(bar(KV_EMPTY0 + st), ((g >> 1) & 1) ^ 1, status, 2);
           if (!alive) break;
+          FMLA_TRACE_AT(g, 0);
           tc::mbar_arrive_expect_tx(bar(KV_FULL0 + st), kTileBytes);
 #pragma unroll
           for (int c = 0; c < 9; ++c)
@@ -152,74 +177,122 @@ decode_dense_tc_kernel(const __grid_constant__ DecodeKernelParams p, const __gri
     // ================================ MMA issuer =======================================
     constexpr uint32_t idesc_s = tc::idesc_bf16_f32(64, 64, 0, 0);
     constexpr uint32_t idesc_o = tc::idesc_bf16_f32(64, 256, 0, 1);
+    // descriptors of the operand bases; per-MMA addresses are constant offsets added to the low word
+    const uint64_t desc_q = tc::smem_desc_sw128(sQ, 16, 1024);             // A of S: K-major
+    const uint64_t desc_k = tc::smem_desc_sw128(sKV, 16, 1024);            // B of S: K-major (stage 0)
+    const uint64_t desc_p = tc::smem_desc_sw128(sP, 16, 1024);             // A of PV: K-major
+    const uint64_t desc_v = tc::smem_desc_sw128(sKV, kChunkBytes, 1024);   // B of PV: MN-major, 64-wide column groups 8 KB apart
     int g = 0, req = 0;
     bool alive = true;
-    auto issue_pv = [&](int gi, bool first_of_request, int req_idx) {
+    // both issue helpers are called by the whole warp; lane 0 issues
+    auto issue_pv = [&](int gi, bool first_of_request) {
       const int st = gi & 1;
-      alive = alive && tc::mbar_wait(bar(P_FULL), gi & 1, status, 3);
-      if (first_of_request) alive = alive && tc::mbar_wait(bar(O_EMPTY), (req_idx & 1) ^ 1, status, 4);
-      alive = __all_sync(0xffffffffu, alive);
-      if (!alive) return;
       tc::tc_fence_after();
-      if (lane == 0) {
-        const uint32_t v_base = sKV + st * kTileBytes;
+      if (lane == 0) FMLA_TRACE_AT(gi, 4);
+      // elect.sync (not a lane-id test) selects the issuing thread: only then does the compiler keep
+      // the descriptors in uniform registers, which halves the per-instruction issue cost
+      if (tc::elect_one()) {
+        // the stage index is resolved by a branch so that every descriptor below is a warp-uniform
+        // base plus an immediate (a runtime stage offset would route each operand through a
+        // vector->uniform register move and halve the issue rate)
+        if (st == 0) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+          for (int h = 0; h < 2; ++h)
 #pragma unroll
-          for (int s = 0; s < 4; ++s) {
-            const uint64_t da = tc::smem_desc_sw128(sP + s * 32, 16, 1024);
-            const uint64_t db = tc::smem_desc_sw128(v_base + h * 4 * kChunkBytes + s * 2048, kChunkBytes, 1024);
-            tc::mma_ws_ss(tmem + TMEM_O + h * 128, da, db, idesc_o, (first_of_request && s == 0) ? 0u : 1u);
-          }
+            for (int s = 0; s < 4; ++s)
+              tc::mma_ws_ss(tmem + TMEM_O + h * 128, tc::desc_advance(desc_p, s * 32),
+                            tc::desc_advance(desc_v, h * 4 * kChunkBytes + s * 2048), idesc_o, (first_of_request && s == 0) ? 0u : 1u);
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+              tc::mma_ws_ss(tmem + TMEM_O + h * 128, tc::desc_advance(desc_p, s * 32),
+                            tc::desc_advance(desc_v, kTileBytes + h * 4 * kChunkBytes + s * 2048), idesc_o, (first_of_request && s == 0) ? 0u : 1u);
+        }
         tc::tc_commit(bar(KV_EMPTY0 + st));
         tc::tc_commit(bar(P_EMPTY));
+        FMLA_TRACE_AT(gi, 5);
       }
       __syncwarp();
     };
+    auto issue_s = [&](int gi, int rows_valid, bool last_of_request) {
+      const int st = gi & 1;
+      // rows of the last page beyond the sequence may hold anything (NaN included): zero them so
+      // that 0 * garbage cannot reach O through P V
+      if (rows_valid < 64) {
+        unsigned char* stage = smem + KV_OFF + st * kTileBytes;
+        const int nrows = 64 - rows_valid;
+        for (int i = lane; i < nrows * 72; i += 32) {
+          const int row = rows_valid + i / 72, c16 = i % 72;
+          *reinterpret_cast<uint4*>(stage + (c16 >> 3) * kChunkBytes + row * 128 + (c16 & 7) * 16) = make_uint4(0, 0, 0, 0);
+        }
+        tc::fence_proxy_async_smem();
+        __syncwarp();
+      }
+      tc::tc_fence_after();
+      if (lane == 0) FMLA_TRACE_AT(gi, 2);
+      if (tc::elect_one()) {
+        if (st == 0) {
+#pragma unroll
+          for (int c = 0; c < 9; ++c)
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+              tc::mma_ws_ss(tmem + TMEM_S, tc::desc_advance(desc_q, c * kChunkBytes + s * 32),
+                            tc::desc_advance(desc_k, c * kChunkBytes + s * 32), idesc_s, (c | s) ? 1u : 0u);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 9; ++c)
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+              tc::mma_ws_ss(tmem + TMEM_S + 32, tc::desc_advance(desc_q, c * kChunkBytes + s * 32),
+                            tc::desc_advance(desc_k, kTileBytes + c * kChunkBytes + s * 32), idesc_s, (c | s) ? 1u : 0u);
+        }
+        tc::tc_commit(bar(S_FULL0 + st));
+        FMLA_TRACE_AT(gi, 3);
+        if (last_of_request) tc::tc_commit(bar(Q_EMPTY));
+      }
+      __syncwarp();
+    };
+    // a poll whose outcome is taken from lane 0, so that the warp stays convergent
+    auto ready = [&](int b, uint32_t parity) { return __shfl_sync(0xffffffffu, tc::mbar_test_wait(bar(b), parity) ? 1 : 0, 0) != 0; };
     for (int batch = begin_idx; batch <= end_idx && alive; ++batch) {
       const ReqInfo r = request_info(p, batch, sq, begin_idx, end_idx, begin_block, end_block, begin_split);
       const int nblk = r.blk_hi - r.blk_lo;
       if (nblk == 0) continue;
       alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_FULL), req & 1, status, 5));
-      const int g0 = g;
-      for (int j = 0; j < nblk && alive; ++j, ++g) {
-        const int st = g & 1;
-        alive = tc::mbar_wait(bar(KV_FULL0 + st), (g >> 1) & 1, status, 6);
-        alive = alive && tc::mbar_wait(bar(S_EMPTY0 + st), ((g >> 1) & 1) ^ 1, status, 7);
-        alive = __all_sync(0xffffffffu, alive);
-        if (!alive) break;
-        // rows of the last page beyond the sequence may hold anything (NaN included): zero them so
-        // that 0 * garbage cannot reach O through P V
-        const int rows_valid = r.seqlen - (r.blk_lo + j) * 64;
-        if (rows_valid < 64) {
-          unsigned char* stage = smem + KV_OFF + st * kTileBytes;
-          const int nrows = 64 - rows_valid;
-          for (int i = lane; i < nrows * 72; i += 32) {
-            const int row = rows_valid + i / 72, c16 = i % 72;
-            *reinterpret_cast<uint4*>(stage + (c16 >> 3) * kChunkBytes + row * 128 + (c16 & 7) * 16) = make_uint4(0, 0, 0, 0);
+      // S of block js and P V of block jp (jp <= js) are issued in whichever order their inputs
+      // become ready, P V first: it releases a cache stage, and the next load depends on that
+      int js = 0, jp = 0, idle = 0;
+      while (jp < nblk && alive) {
+        bool did = false;
+        if (jp < js) {
+          const int gi = g + jp;
+          if (ready(P_FULL, gi & 1) && (jp > 0 || ready(O_EMPTY, (req & 1) ^ 1))) {
+            issue_pv(gi, jp == 0);
+            ++jp;
+            did = true;
           }
-          tc::fence_proxy_async_smem();
-          __syncwarp();
         }
-        tc::tc_fence_after();
-        if (lane == 0) {
-          const uint32_t k_base = sKV + st * kTileBytes;
-#pragma unroll
-          for (int c = 0; c < 9; ++c)
-#pragma unroll
-            for (int s = 0; s < 4; ++s) {
-              const uint64_t da = tc::smem_desc_sw128(sQ + c * kChunkBytes + s * 32, 16, 1024);
-              const uint64_t db = tc::smem_desc_sw128(k_base + c * kChunkBytes + s * 32, 16, 1024);
-              tc::mma_ws_ss(tmem + TMEM_S + st * 32, da, db, idesc_s, (c | s) ? 1u : 0u);
-            }
-          tc::tc_commit(bar(S_FULL0 + st));
-          if (j == nblk - 1) tc::tc_commit(bar(Q_EMPTY));
+        if (!did && js < nblk) {
+          const int gi = g + js, st = gi & 1;
+          if (ready(KV_FULL0 + st, (gi >> 1) & 1) && ready(S_EMPTY0 + st, ((gi >> 1) & 1) ^ 1)) {
+            issue_s(gi, r.seqlen - (r.blk_lo + js) * 64, js == nblk - 1);
+            ++js;
+            did = true;
+          }
         }
-        __syncwarp();
-        if (j >= 1) issue_pv(g - 1, j == 1, req);
+        if (did) {
+          idle = 0;
+        } else if (++idle > tc::kSpinLimit) {
+          if (lane == 0) atomicCAS(status, 0, 6);
+          alive = false;
+        } else {
+          __nanosleep(32);   // a tight poll would take issue slots from the softmax warp on this scheduler
+        }
       }
-      if (alive) issue_pv(g0 + nblk - 1, nblk == 1, req);
-      if (alive && lane == 0) tc::tc_commit(bar(O_FULL));
+      g += nblk;
+      if (alive && tc::elect_one()) tc::tc_commit(bar(O_FULL));
       __syncwarp();
       ++req;
     }
@@ -240,6 +313,7 @@ decode_dense_tc_kernel(const __grid_constant__ DecodeKernelParams p, const __gri
         const int st = g & 1;
         uint32_t sv[32];
         if (tc::mbar_wait(bar(S_FULL0 + st), (g >> 1) & 1, status, 8)) {
+          if (tid == 0) FMLA_TRACE_AT(g, 6);
           tc::tc_fence_after();
           tc::tmem_ld32(tmem + lane_addr + TMEM_S + st * 32, sv);
           tc::tmem_wait_ld();
@@ -250,6 +324,7 @@ decode_dense_tc_kernel(const __grid_constant__ DecodeKernelParams p, const __gri
           for (int i = 0; i < 32; ++i) sv[i] = 0u;
         }
         tc::mbar_arrive(bar(S_EMPTY0 + st));
+        if (tid == 0) FMLA_TRACE_AT(g, 7);
 
         const int tok0 = (r.blk_lo + j) * 64 + th * 32;
         float s[32];
@@ -271,6 +346,7 @@ decode_dense_tc_kernel(const __grid_constant__ DecodeKernelParams p, const __gri
         xch[tid] = mx;
         bar_sync(1, 128);
         if (*sAbort) { aborted = true; break; }
+        if (tid == 0) FMLA_TRACE_AT(g, 8);
         mx = fmaxf(mx, xch[tid ^ 64]);
         const float m_new = fmaxf(m_run, mx);
 
@@ -283,9 +359,11 @@ decode_dense_tc_kernel(const __grid_constant__ DecodeKernelParams p, const __gri
           need = (m_new - m_used) > kRescaleThreshold || (m_run == neg_inf() && m_new != neg_inf());
         }
         m_run = m_new;
-        // the previous P V must be complete before P is overwritten and before O may be rescaled
-        if (!tc::mbar_wait(bar(P_EMPTY), (g & 1) ^ 1, status, 9)) *sAbort = 1;
-        if (__any_sync(0xffffffffu, need)) {
+        const bool any_need = __any_sync(0xffffffffu, need);
+        bool pv_done = false;    // the previous P V must be complete before O is rescaled and before P is overwritten
+        if (any_need) {
+          if (!tc::mbar_wait(bar(P_EMPTY), (g & 1) ^ 1, status, 9)) *sAbort = 1;
+          pv_done = true;
           const float m_next = need ? m_new : m_used;
           const float alpha = exp2f(m_used - m_next);
           m_used = m_next;
@@ -303,6 +381,7 @@ decode_dense_tc_kernel(const __grid_constant__ DecodeKernelParams p, const __gri
           tc::tmem_wait_st();
           tc::tc_fence_before();
         }
+        if (tid == 0) FMLA_TRACE_AT(g, 10);
         float rs = 0.f;
         uint32_t pk[16];
 #pragma unroll
@@ -312,6 +391,8 @@ decode_dense_tc_kernel(const __grid_constant__ DecodeKernelParams p, const __gri
           pk[i] = pack_bf16x2(p0, p1);
         }
         l_part += rs;
+        if (!pv_done && !tc::mbar_wait(bar(P_EMPTY), (g & 1) ^ 1, status, 9)) *sAbort = 1;
+        if (tid == 0) FMLA_TRACE_AT(g, 9);
         // P[row][th*32 .. +32) -> K-major 128B-swizzled A operand: 16-byte chunk (th*4 + q) ^ (row & 7)
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
@@ -320,6 +401,7 @@ decode_dense_tc_kernel(const __grid_constant__ DecodeKernelParams p, const __gri
         }
         tc::fence_proxy_async_smem();
         tc::mbar_arrive(bar(P_FULL));
+        if (tid == 0) FMLA_TRACE_AT(g, 11);
       }
 
       // ---- epilogue of this request --------------------------------------------------
@@ -435,6 +517,12 @@ cudaError_t launch_decode_dense_tc(const DecodeKernelParams& p, cudaStream_t str
   kern<<<grid, 192, dtc::SMEM_BYTES, stream>>>(p, tq, tkv);
   return cudaGetLastError();
 }
+
+#ifdef FMLA_TRACE
+extern "C" int fmla_debug_read_trace(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_decode_trace, sizeof(long long) * n);
+}
+#endif
 
 cudaError_t read_decode_tc_status(int* host_status, bool reset) {
   cudaError_t e = cudaMemcpyFromSymbol(host_status, g_decode_tc_status, sizeof(int));
