@@ -71,6 +71,8 @@ SYMBOLS = {
     "fmla_decode_scratch_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                             C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "fmla_fwd_kvcache_mla": (C.c_int, [C.POINTER(DecodeParams), vp]),
+    "fmla_fwd_kvcache_mla_static_scratch": (C.c_int, [C.POINTER(DecodeParams), vp]),
+    "fmla_static_scratch_max_rows": (C.c_size_t, []),
     "fmla_combine_partials": (C.c_int, [vp, vp, C.c_int, C.c_int, C.c_int, vp, i64, vp, vp]),
     "fmla_sparse_prefill_fwd": (C.c_int, [C.POINTER(SparsePrefillParams), vp]),
     "fmla_dense_prefill_fwd": (C.c_int, [C.POINTER(DenseParams), vp]),

@@ -71,6 +71,11 @@ int require_blackwell() {
 
 }  // namespace
 
+namespace fmla {
+// lets other translation units of the library report through the same thread-local message
+int set_error(int code, const char* message) { return fail(code, "%s", message); }
+}  // namespace fmla
+
 extern "C" {
 
 const char* fmla_status_string(int status) {

@@ -66,6 +66,9 @@ struct DenseKernelParams {
   float* dq_acc;     // workspace (unused by the deterministic dQ pass)
 };
 
+// records `message` as the calling thread's last error and returns `code`
+int set_error(int code, const char* message);
+
 cudaError_t launch_get_mla_metadata(const int* seqlens_k, int batch, int num_sm_parts, int topk, int* md,
                                     int* num_splits, cudaStream_t stream);
 cudaError_t launch_decode_mma(const DecodeKernelParams& p, cudaStream_t stream);

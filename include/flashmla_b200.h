@@ -128,6 +128,31 @@ int fmla_decode_scratch_bytes(int b, int s_q, int h_q, int num_sm_parts, int d_v
 
 int fmla_fwd_kvcache_mla(const fmla_decode_params* params_host, void* stream);
 
+/* Same computation as fmla_fwd_kvcache_mla for callers that must not allocate
+ * (this entry point has no counterpart in the reference, whose extension always
+ * allocates its accumulators with torch, csrc/pybind.cpp:574-581).
+ *
+ * Who needs it: a host that gives out device memory only at start-up (a fixed
+ * arena, a plugin "enqueue" hook, a loop that is being recorded into a stream)
+ * cannot size and allocate the split-KV scratch per call, and cudaMalloc there
+ * would either be refused or stall the device.  Here the scratch lives in the
+ * library image: params->lse_accum and params->o_accum are IGNORED and replaced
+ * by two built-in device arrays; inputs and outputs are still the caller's.
+ *
+ *  - limit: (b + num_sm_parts) * s_q * h_q  <=  fmla_static_scratch_max_rows()
+ *    (32768 rows, i.e. 64 MiB + 128 KiB held by every GPU that loads the library
+ *    until the process exits); larger problems are rejected with
+ *    FMLA_ERR_INVALID_ARGUMENT and a message naming both numbers;
+ *  - the first call on each device looks up the arrays' device addresses
+ *    (cudaGetSymbolAddress); make that first call before recording work into a
+ *    stream, later calls only launch kernels;
+ *  - every call on a GPU uses the same arrays: calls that overlap on the GPU
+ *    (different streams or threads) race on them; serialise them.  Nothing has
+ *    to be cleared between calls: each call overwrites every slot it later reads;
+ *  - it performs no cudaMalloc / cudaFree and calls no allocating routine. */
+int fmla_fwd_kvcache_mla_static_scratch(const fmla_decode_params* params_host, void* stream);
+size_t fmla_static_scratch_max_rows(void);
+
 /* ------------------------------------------------------------------------- *
  * Stand-alone log-sum-exp merge of normalised partial results.
  * Replaces run_flash_mla_combine_kernel (csrc/smxx/mla_combine.cu:170-195) and
