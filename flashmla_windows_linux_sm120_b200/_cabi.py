@@ -60,6 +60,11 @@ class DenseParams(C.Structure):
     ]
 
 
+class PeerPush(C.Structure):
+    _fields_ = [("slot", i32), ("num_dst", i32), ("dst_o", vp * 8), ("dst_lse", vp * 8), ("dst_flag", vp * 8),
+                ("epoch", C.c_uint32), ("counter", vp)]
+
+
 # every symbol include/flashmla_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "fmla_status_string": (C.c_char_p, [C.c_int]),
@@ -73,6 +78,9 @@ SYMBOLS = {
     "fmla_fwd_kvcache_mla": (C.c_int, [C.POINTER(DecodeParams), vp]),
     "fmla_fwd_kvcache_mla_static_scratch": (C.c_int, [C.POINTER(DecodeParams), vp]),
     "fmla_static_scratch_max_rows": (C.c_size_t, []),
+    "fmla_fwd_kvcache_mla_push_partial": (C.c_int, [C.POINTER(DecodeParams), C.POINTER(PeerPush), vp]),
+    "fmla_merge_peer_partials": (C.c_int, [vp, vp, C.c_int, C.c_int, C.c_int, vp, C.c_uint32, C.c_int, vp, i64, vp, vp]),
+    "fmla_sizeof_peer_push": (C.c_size_t, []),
     "fmla_combine_partials": (C.c_int, [vp, vp, C.c_int, C.c_int, C.c_int, vp, i64, vp, vp]),
     "fmla_sparse_prefill_fwd": (C.c_int, [C.POINTER(SparsePrefillParams), vp]),
     "fmla_dense_prefill_fwd": (C.c_int, [C.POINTER(DenseParams), vp]),
@@ -98,7 +106,7 @@ def _load() -> C.CDLL:
         fn.argtypes = args
     for cls, fn in ((DecodeParams, lib.fmla_sizeof_decode_params),
                     (SparsePrefillParams, lib.fmla_sizeof_sparse_prefill_params),
-                    (DenseParams, lib.fmla_sizeof_dense_params)):
+                    (DenseParams, lib.fmla_sizeof_dense_params), (PeerPush, lib.fmla_sizeof_peer_push)):
         if C.sizeof(cls) != fn():
             raise ImportError(f"struct layout mismatch for {cls.__name__}: {C.sizeof(cls)} vs {fn()}")
     return lib

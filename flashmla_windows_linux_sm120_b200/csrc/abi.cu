@@ -95,6 +95,7 @@ const char* fmla_variant(void) { return "sm100a"; }
 size_t fmla_sizeof_decode_params(void) { return sizeof(fmla_decode_params); }
 size_t fmla_sizeof_sparse_prefill_params(void) { return sizeof(fmla_sparse_prefill_params); }
 size_t fmla_sizeof_dense_params(void) { return sizeof(fmla_dense_params); }
+size_t fmla_sizeof_peer_push(void) { return sizeof(fmla_peer_push); }
 
 int fmla_get_num_sm_parts(int device, int num_q_tokens_per_head_k, int h_k, int h_q, int is_fp8_kvcache, int is_sparse,
                           int* num_sm_parts_host) {
@@ -139,7 +140,7 @@ int fmla_decode_scratch_bytes(int b, int s_q, int h_q, int num_sm_parts, int d_v
   return FMLA_OK;
 }
 
-int fmla_fwd_kvcache_mla(const fmla_decode_params* P, void* stream) {
+static int decode_impl(const fmla_decode_params* P, const fmla_peer_push* push, void* stream) {
   FMLA_REQUIRE(P != nullptr, "params is null");
   const fmla_decode_params& a = *P;
   const bool sparse = a.topk >= 0;
@@ -151,7 +152,8 @@ int fmla_fwd_kvcache_mla(const fmla_decode_params* P, void* stream) {
   FMLA_REQUIRE(a.h_q % a.h_k == 0, "Number of heads in key/value must divide number of heads in query");
   if (a.q_dtype != FMLA_DTYPE_BF16) return fail(FMLA_ERR_UNSUPPORTED, "only bfloat16 queries are supported");
   if (sparse != (a.is_fp8 != 0)) return fail(FMLA_ERR_UNSUPPORTED, "supported combinations: dense BF16 cache, or sparse (indices) FP8 cache");
-  FMLA_REQUIRE(a.q && a.kcache && a.seqlens_k && a.tile_scheduler_metadata && a.num_splits && a.out && a.softmax_lse && a.lse_accum && a.o_accum, "null pointer");
+  FMLA_REQUIRE(a.q && a.kcache && a.seqlens_k && a.tile_scheduler_metadata && a.num_splits && a.lse_accum && a.o_accum, "null pointer");
+  FMLA_REQUIRE(push || (a.out && a.softmax_lse), "null output pointer");
   FMLA_REQUIRE(a.num_sm_parts > 0, "num_sm_parts must be positive");
   FMLA_REQUIRE(aligned16(a.q) && aligned16(a.kcache) && aligned16(a.out) && aligned16(a.o_accum) && aligned16(a.tile_scheduler_metadata), "q, kcache, out, o_accum and tile_scheduler_metadata must be 16-byte aligned");
   FMLA_REQUIRE(a.q_stride_b % 8 == 0 && a.q_stride_s % 8 == 0 && a.q_stride_h % 8 == 0, "q strides must be multiples of 8 elements");
@@ -185,6 +187,11 @@ int fmla_fwd_kvcache_mla(const fmla_decode_params* P, void* stream) {
   k.tile_scheduler_metadata = a.tile_scheduler_metadata; k.num_sm_parts = a.num_sm_parts; k.num_splits = a.num_splits;
   k.out = a.out; k.o_stride_b = a.o_stride_b; k.o_stride_s = a.o_stride_s; k.o_stride_h = a.o_stride_h;
   k.softmax_lse = a.softmax_lse; k.lse_accum = a.lse_accum; k.o_accum = a.o_accum;
+  if (push) {
+    k.force_partial = 1;
+    k.push_slot = push->slot; k.push_num_dst = push->num_dst; k.push_epoch = push->epoch; k.push_counter = push->counter;
+    for (int d = 0; d < push->num_dst; ++d) { k.push_o[d] = push->dst_o[d]; k.push_lse[d] = push->dst_lse[d]; k.push_flag[d] = push->dst_flag[d]; }
+  }
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
@@ -203,9 +210,37 @@ int fmla_fwd_kvcache_mla(const fmla_decode_params* P, void* stream) {
     e = cudaEventRecord(static_cast<cudaEvent_t>(a.profile_event_end), s);
     if (e != cudaSuccess) return cuda_fail(e, "cudaEventRecord");
   }
-  e = fmla::launch_decode_combine(k, s);
+  if (push) {
+    FMLA_REQUIRE(!sparse, "the peer push is implemented for the dense decode");
+    e = fmla::launch_decode_combine_push(k, s);
+  } else {
+    e = fmla::launch_decode_combine(k, s);
+  }
   if (e != cudaSuccess) return cuda_fail(e, "decode combine launch");
   return FMLA_OK;
+}
+
+int fmla_fwd_kvcache_mla(const fmla_decode_params* P, void* stream) { return decode_impl(P, nullptr, stream); }
+
+int fmla_fwd_kvcache_mla_push_partial(const fmla_decode_params* P, const fmla_peer_push* push, void* stream) {
+  FMLA_REQUIRE(push != nullptr, "push is null");
+  FMLA_REQUIRE(push->num_dst >= 1 && push->num_dst <= 8, "num_dst must be in 1..8");
+  FMLA_REQUIRE(push->slot >= 0 && push->counter != nullptr, "slot must be >= 0 and counter non-null");
+  for (int d = 0; d < push->num_dst; ++d)
+    FMLA_REQUIRE(push->dst_o[d] && push->dst_lse[d] && push->dst_flag[d] && aligned16(push->dst_o[d]), "destination pointers must be non-null, dst_o 16-byte aligned");
+  return decode_impl(P, push, stream);
+}
+
+int fmla_merge_peer_partials(const float* part_lse, const float* part_o, int num_parts, int rows, int d_v, const uint32_t* flags,
+                             uint32_t epoch, int max_polls, void* out, int64_t o_stride_row, float* lse, void* stream) {
+  FMLA_REQUIRE(part_lse && part_o && flags && out && lse, "null pointer");
+  FMLA_REQUIRE(num_parts > 0 && num_parts <= 4096 && rows > 0, "num_parts must be in 1..4096 and rows positive");
+  FMLA_REQUIRE(d_v == 512, "Only head_size_v == 512 is supported");
+  FMLA_REQUIRE(max_polls > 0, "max_polls must be positive");
+  FMLA_REQUIRE(aligned16(part_o) && aligned16(out) && o_stride_row % 8 == 0, "part_o/out must be 16-byte aligned, stride a multiple of 8");
+  cudaError_t e = fmla::launch_merge_peer_partials(part_lse, part_o, num_parts, rows, out, o_stride_row, lse, flags, epoch, max_polls,
+                                                  static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FMLA_OK : cuda_fail(e, "peer merge launch");
 }
 
 int fmla_combine_partials(const float* lse_accum, const float* o_accum, int num_parts, int rows, int d_v, void* out,
@@ -317,6 +352,10 @@ int fmla_device_status(int* status_host, int reset) {
   FMLA_REQUIRE(status_host != nullptr, "status_host is null");
   cudaError_t e = fmla::read_decode_tc_status(status_host, reset != 0);
   if (e != cudaSuccess) return cuda_fail(e, "reading the device status word");
+  int merge_status = 0;
+  e = fmla::read_merge_status(&merge_status, reset != 0);
+  if (e != cudaSuccess) return cuda_fail(e, "reading the device status word");
+  if (*status_host == 0) *status_host = merge_status;
   return *status_host == 0 ? FMLA_OK : fail(FMLA_ERR_DEVICE_TIMEOUT, "a bounded device-side wait expired (code %d)", *status_host);
 }
 

@@ -95,6 +95,143 @@ combine_partials_kernel(const float* __restrict__ lse_accum, const float* __rest
       lse + r);
 }
 
+// ---- KV-sharded decode across GPUs ---------------------------------------------------------------
+// Each rank merges its local splits per row and stores the normalised fp32 result + base-2 LSE
+// into its slot of every destination's partial buffers with plain (peer) stores; the last CTA to
+// finish publishes the epoch in the destinations' flag words (release, system scope).
+__device__ __forceinline__ void st_release_sys(unsigned int* addr, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* addr) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(kCombineWarps * 32) decode_combine_push_kernel(const __grid_constant__ DecodeKernelParams p) {
+  extern __shared__ float s_weights[];  // [8][num_sm_parts]
+  const int batch = blockIdx.x;
+  const int lo = __ldg(p.num_splits + batch), hi = __ldg(p.num_splits + batch + 1);
+  const int nparts = hi - lo;
+  const int q_seq_per_hk = p.s_q * p.hq_per_hk;
+  const int rows = p.h_k * q_seq_per_hk;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.y * kCombineWarps + warp;
+  if (r < rows) {
+    const float* lse_base = p.lse_accum + (int64_t)lo * rows + r;
+    const float* o_base = p.o_accum + ((int64_t)lo * rows + r) * 512;
+    float* w = s_weights + warp * p.num_sm_parts;
+    float mx = neg_inf();
+    for (int i = lane; i < nparts; i += 32) mx = fmaxf(mx, __ldg(lse_base + (int64_t)i * rows));
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    const float mref = mx == neg_inf() ? 0.f : mx;
+    float sum = 0.f;
+    for (int i = lane; i < nparts; i += 32) sum += exp2f(__ldg(lse_base + (int64_t)i * rows) - mref);
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    const float glse = (sum == 0.f || sum != sum) ? neg_inf() : log2f(sum) + mref;   // base 2, -inf = empty shard
+    for (int i = lane; i < nparts; i += 32) w[i] = glse == neg_inf() ? 0.f : exp2f(__ldg(lse_base + (int64_t)i * rows) - glse);
+    __syncwarp();
+    float4 acc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < nparts; ++i) {
+      const float wi = w[i];
+      if (wi == 0.f) continue;
+      const float4* src = reinterpret_cast<const float4*>(o_base + (int64_t)i * rows * 512);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 v = __ldg(src + j * 32 + lane);
+        acc[j].x += wi * v.x; acc[j].y += wi * v.y; acc[j].z += wi * v.z; acc[j].w += wi * v.w;
+      }
+    }
+    const int64_t total_rows = (int64_t)p.b * rows;
+    const int64_t grow = (int64_t)p.push_slot * total_rows + (int64_t)batch * rows + r;
+    for (int d = 0; d < p.push_num_dst; ++d) {
+      float4* dst = reinterpret_cast<float4*>(p.push_o[d] + grow * 512);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) dst[j * 32 + lane] = acc[j];
+      if (lane == 0) p.push_lse[d][grow] = glse;
+    }
+  }
+  // publish: every thread's peer stores are ordered before the flag by fence + barrier + release
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int total = gridDim.x * gridDim.y;
+    const unsigned int done = atomicAdd(p.push_counter, 1u) + 1u;
+    if (done == total) {
+      __threadfence_system();
+      for (int d = 0; d < p.push_num_dst; ++d) st_release_sys(p.push_flag[d] + p.push_slot, p.push_epoch);
+      *p.push_counter = 0u;
+    }
+  }
+}
+
+// Merge of per-rank partials that arrive through peer stores: wait (bounded) for every rank's flag.
+__global__ void __launch_bounds__(kCombineWarps * 32)
+merge_peer_partials_kernel(const float* __restrict__ lse_accum, const float* __restrict__ o_accum, int nparts, int rows,
+                           __nv_bfloat16* __restrict__ out, int64_t o_stride_row, float* __restrict__ lse,
+                           const unsigned int* __restrict__ flags, unsigned int epoch, int max_polls, int* status) {
+  extern __shared__ float s_weights[];  // [8][nparts]
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int i = 0; i < nparts && ok; ++i) {
+      int polls = 0;
+      while (ld_acquire_sys(flags + i) != epoch) {
+        if (++polls > max_polls) { ok = 0; break; }
+        __nanosleep(200);
+      }
+    }
+    if (!ok) atomicCAS(status, 0, 20);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;     // the caller reads the status word; outputs are left untouched
+  const int warp = threadIdx.x >> 5;
+  const int r = blockIdx.x * kCombineWarps + warp;
+  if (r >= rows) return;
+  combine_row(
+      nparts, [&](int i) { return __ldcv(lse_accum + (int64_t)i * rows + r); },
+      [&](int i) { return o_accum + ((int64_t)i * rows + r) * 512; }, s_weights + warp * nparts, out + r * o_stride_row,
+      lse + r);
+}
+
+__device__ int g_merge_status = 0;
+
+cudaError_t launch_decode_combine_push(const DecodeKernelParams& p, cudaStream_t stream) {
+  const int rows = p.h_k * p.s_q * p.hq_per_hk;
+  dim3 grid(p.b, (rows + kCombineWarps - 1) / kCombineWarps);
+  const size_t smem = sizeof(float) * kCombineWarps * p.num_sm_parts;
+  decode_combine_push_kernel<<<grid, kCombineWarps * 32, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_merge_peer_partials(const float* lse_accum, const float* o_accum, int num_parts, int rows, void* out,
+                                       int64_t o_stride_row, float* lse, const unsigned int* flags, unsigned int epoch,
+                                       int max_polls, cudaStream_t stream) {
+  int* status = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_merge_status);
+  if (e != cudaSuccess) return e;
+  const size_t smem = sizeof(float) * kCombineWarps * num_parts;
+  merge_peer_partials_kernel<<<(rows + kCombineWarps - 1) / kCombineWarps, kCombineWarps * 32, smem, stream>>>(
+      lse_accum, o_accum, num_parts, rows, reinterpret_cast<__nv_bfloat16*>(out), o_stride_row, lse, flags, epoch, max_polls,
+      status);
+  return cudaGetLastError();
+}
+
+cudaError_t read_merge_status(int* host_status, bool reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(host_status, g_merge_status, sizeof(int));
+  if (e != cudaSuccess) return e;
+  if (reset && *host_status != 0) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_merge_status, &zero, sizeof(int));
+  }
+  return e;
+}
+
 cudaError_t launch_decode_combine(const DecodeKernelParams& p, cudaStream_t stream) {
   const int rows = p.h_k * p.s_q * p.hq_per_hk;
   dim3 grid(p.b, (rows + kCombineWarps - 1) / kCombineWarps);

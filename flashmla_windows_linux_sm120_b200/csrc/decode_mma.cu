@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(256, 1) decode_splitkv_kernel(const __grid_con
     const int blk_hi = min(batch == end_idx ? end_block : nblk_total, nblk_total);
     const int n_split_idx = batch == begin_idx ? begin_split : 0;
     const int split_lo = __ldg(p.num_splits + batch);
-    const bool no_split = __ldg(p.num_splits + batch + 1) - split_lo == 1;
+    const bool no_split = !p.force_partial && __ldg(p.num_splits + batch + 1) - split_lo == 1;
 
     TileAcc<DecodeCfg> acc;
     run_tile<DecodeCfg>(prob, smem, blk_lo, blk_hi, p.scale_log2, acc);

@@ -73,7 +73,7 @@ __device__ __forceinline__ ReqInfo request_info(const DecodeKernelParams& p, int
   r.blk_hi = min(min(batch == end_idx ? end_block : nblk_total, nblk_total), nblk_visible);
   if (r.blk_hi < r.blk_lo) r.blk_hi = r.blk_lo;
   const int lo = __ldg(p.num_splits + batch);
-  r.no_split = __ldg(p.num_splits + batch + 1) - lo == 1;
+  r.no_split = !p.force_partial && __ldg(p.num_splits + batch + 1) - lo == 1;
   r.split_slot = lo + (batch == begin_idx ? begin_split : 0);
   return r;
 }

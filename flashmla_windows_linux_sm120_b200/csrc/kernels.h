@@ -31,6 +31,16 @@ struct DecodeKernelParams {
   float* softmax_lse;
   float* lse_accum;
   float* o_accum;
+  // KV-sharded decode across GPUs: every request goes through the accumulators (force_partial) and the
+  // merge of the local splits is pushed, as a normalised fp32 partial, into slot `push_slot` of each
+  // destination's partial buffers (peer-mapped device memory), followed by a flag store.
+  int force_partial;
+  int push_slot, push_num_dst;
+  float* push_o[8];            // [num_slots][b * h_k * rows][512]
+  float* push_lse[8];          // [num_slots][b * h_k * rows], base 2
+  unsigned int* push_flag[8];  // [num_slots]
+  unsigned int push_epoch;
+  unsigned int* push_counter;  // local counter of finished CTAs (zero on entry, left zero)
 };
 
 struct SparsePrefillKernelParams {
@@ -81,6 +91,13 @@ cudaError_t launch_decode_combine(const DecodeKernelParams& p, cudaStream_t stre
 // Stand-alone merge of num_parts partial slots for `rows` rows.
 cudaError_t launch_combine_partials(const float* lse_accum, const float* o_accum, int num_parts, int rows, void* out,
                                     int64_t o_stride_row, float* lse, cudaStream_t stream);
+// merge of local splits + push of the result to peers (see DecodeKernelParams::push_*)
+cudaError_t launch_decode_combine_push(const DecodeKernelParams& p, cudaStream_t stream);
+// merge that first waits (bounded) until flags[i] == epoch for every part
+cudaError_t launch_merge_peer_partials(const float* lse_accum, const float* o_accum, int num_parts, int rows, void* out,
+                                       int64_t o_stride_row, float* lse, const unsigned int* flags, unsigned int epoch,
+                                       int max_polls, cudaStream_t stream);
+cudaError_t read_merge_status(int* host_status, bool reset);
 cudaError_t launch_sparse_prefill_mma(const SparsePrefillKernelParams& p, cudaStream_t stream);
 cudaError_t launch_dense_fwd_mma(const DenseKernelParams& p, cudaStream_t stream);
 cudaError_t launch_dense_bwd_mma(const DenseKernelParams& p, cudaStream_t stream);

@@ -166,6 +166,41 @@ int fmla_combine_partials(const float* lse_accum, const float* o_accum, int num_
                           int d_v, void* out, int64_t o_stride_row, float* lse, void* stream);
 
 /* ------------------------------------------------------------------------- *
+ * KV-sharded decode across GPUs (one long context whose cache pages are split
+ * over N ranks).  No counterpart in the reference, which is single-GPU; the
+ * math is its split-KV merge (csrc/smxx/mla_combine.cu:71-151) applied to
+ * per-rank partials instead of per-SM partials.
+ *
+ * fmla_fwd_kvcache_mla_push_partial: runs the dense decode over this rank's
+ * shard, merges the local splits and stores the normalised fp32 partial O
+ * [b*h_q*s_q rows, 512] and its base-2 LSE into slot `slot` of every
+ * destination's buffers (device pointers that may be peer-mapped memory of other
+ * GPUs: plain stores over NVLink), then publishes `epoch` in dst_flag[d][slot]
+ * with a system-scope release.  params->out / softmax_lse are not written.
+ * `counter` is a zero-initialised device word owned by this rank.
+ *
+ * fmla_merge_peer_partials: waits (at most max_polls polls of ~200 ns per flag)
+ * until flags[i] == epoch for all i < num_parts, then merges the parts like
+ * fmla_combine_partials.  If a flag never arrives the kernel leaves the outputs
+ * untouched and sets the device status word (fmla_device_status reports
+ * FMLA_ERR_DEVICE_TIMEOUT); it does not hang.
+ * ------------------------------------------------------------------------- */
+typedef struct fmla_peer_push {
+  int32_t slot;              /* this rank's slot in the destinations' buffers */
+  int32_t num_dst;           /* 1..8                                          */
+  float* dst_o[8];           /* [num_slots][rows][512] fp32                   */
+  float* dst_lse[8];         /* [num_slots][rows] fp32, base 2                */
+  uint32_t* dst_flag[8];     /* [num_slots]                                   */
+  uint32_t epoch;            /* value published in the flags (change it every step) */
+  uint32_t* counter;         /* local scratch word, zero before the first call */
+} fmla_peer_push;
+
+int fmla_fwd_kvcache_mla_push_partial(const fmla_decode_params* params_host, const fmla_peer_push* push_host, void* stream);
+int fmla_merge_peer_partials(const float* part_lse, const float* part_o, int num_parts, int rows, int d_v,
+                             const uint32_t* flags, uint32_t epoch, int max_polls, void* out, int64_t o_stride_row,
+                             float* lse, void* stream);
+
+/* ------------------------------------------------------------------------- *
  * Sparse MLA prefill forward.  Replaces sparse_prefill_fwd
  * (csrc/pybind.cpp:730-814) -> sm100::run_fwd_kernel
  * (csrc/sm100/prefill/sparse/fwd.cu:705-783).  Mirrors SparsePrefillParams
@@ -241,6 +276,7 @@ int fmla_device_status(int* status_host, int reset);
 size_t fmla_sizeof_decode_params(void);
 size_t fmla_sizeof_sparse_prefill_params(void);
 size_t fmla_sizeof_dense_params(void);
+size_t fmla_sizeof_peer_push(void);
 
 #ifdef __cplusplus
 }
