@@ -82,8 +82,10 @@ int set_error(int code, const char* message);
 cudaError_t launch_get_mla_metadata(const int* seqlens_k, int batch, int num_sm_parts, int topk, int* md,
                                     int* num_splits, cudaStream_t stream);
 cudaError_t launch_decode_mma(const DecodeKernelParams& p, cudaStream_t stream);
-// dense BF16 decode on tcgen05 / TMA (decode_tc.cu)
+// tcgen05 / TMA / TMEM kernels (mla_tc.cu): dense decode, sparse FP8 decode, sparse prefill
 cudaError_t launch_decode_dense_tc(const DecodeKernelParams& p, cudaStream_t stream);
+cudaError_t launch_decode_sparse_tc(const DecodeKernelParams& p, cudaStream_t stream);
+cudaError_t launch_sparse_prefill_tc(const SparsePrefillKernelParams& p, cudaStream_t stream);
 // reads (and optionally clears) the status word the tcgen05 kernels set when a bounded wait expires
 cudaError_t read_decode_tc_status(int* host_status, bool reset);
 // Merge of split partials for a decode call (reads num_splits; skips unsplit requests).
