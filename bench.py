@@ -109,7 +109,7 @@ class DenseDecode:
     """BASELINE config 2: dense BF16 MLA decode at the DeepSeek-V3 shape."""
     metric, unit, dtype = "dense_bf16_mla_decode_bandwidth", "GB/s", "bf16"
     bound = "hbm"
-    kernel_name = "decode_dense_tc_kernel"
+    kernel_name = "mla_tc_kernel<kDense>"
     launches_per_step = 2          # split-KV attention + combine
 
     def __init__(self, s_q: int = 1, batch: int = 128, h_q: int = 128):
@@ -200,7 +200,7 @@ class SparseDecode:
     """BASELINE config 3: sparse FP8 MLA decode, batch 64, top-k 2048 of 32768 cached tokens."""
     metric, unit, dtype = "sparse_fp8_mla_decode_tflops", "TFLOP/s", "bf16 (fp8 e4m3 cache)"
     bound = "tensor"
-    kernel_name = "decode_splitkv_kernel<sparse>"
+    kernel_name = "mla_tc_kernel<kSparseDecode>"
     launches_per_step = 2
 
     def __init__(self, batch: int = 64, topk: int = 2048, seqlen: int = 32768, h_q: int = 128):
@@ -251,7 +251,7 @@ class SparsePrefill:
     """BASELINE config 4: sparse MLA prefill forward, s_q 4096, s_kv 32768, top-k 2048 (causally restricted)."""
     metric, unit, dtype = "sparse_mla_prefill_fwd_tflops", "TFLOP/s", "bf16"
     bound = "tensor"
-    kernel_name = "sparse_prefill_kernel"
+    kernel_name = "mla_tc_kernel<kSparsePrefill>"
     launches_per_step = 1
 
     def __init__(self, s_q: int = 4096, s_kv: int = 32768, topk: int = 2048, h_q: int = 128):

@@ -3,7 +3,7 @@
 //   kSparseDecode  sparse FP8 split-KV decode: top-k slot indices, 656-byte records gathered and
 //                  de-quantised to bf16 in shared memory by eight producer warps
 //   kSparsePrefill sparse prefill forward: top-k row indices into kv[s_kv, 576], rows gathered with
-//                  cp.async by four producer warps
+//                  cp.async by eight producer warps
 //
 // One CTA = the 64-head tile of one query token.
 //   warps 0-3 softmax : TMEM S -> registers, mask, running max / sum (base 2), P (bf16) -> shared
@@ -13,7 +13,7 @@
 //   warp 5   MMA      : S = Q K^T  (36 x tcgen05.mma.ws m64n64k16)  -> TMEM S[stage]
 //                       O += P V   ( 8 x tcgen05.mma.ws m64n256k16) -> TMEM O
 //                       V is the first 512 columns of the same K tile, read MN-major
-//   warps 6..  gather : sparse modes only (4 warps for prefill, 8 for FP8 decode); write K rows in exactly the layout TMA produces
+//   warps 6-13 gather : sparse modes only; write K rows in exactly the layout TMA produces
 //                       (64-column chunks of 128-byte rows, 128-byte swizzle), so the MMA side is
 //                       the same for all three uses
 // TMEM map (512 columns allocated): O = [0,256) (two N=256 halves of 128 columns),
@@ -56,10 +56,13 @@ enum Bar { Q_FULL = 0, Q_EMPTY, KV_FULL0, KV_FULL1, KV_EMPTY0, KV_EMPTY1, S_FULL
 constexpr int TMEM_O = 0, TMEM_S = 256;
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory limit per CTA");
 static_assert(NUM_BARS * 8 <= 128, "barrier area too small");
-constexpr int kPrefetchDist = 6;                  // cache pages prefetched into L2 ahead of the stage loads
+#ifndef FMLA_PREFETCH_DIST
+#define FMLA_PREFETCH_DIST 6
+#endif
+constexpr int kPrefetchDist = FMLA_PREFETCH_DIST; // cache pages prefetched into L2 ahead of the stage loads
 constexpr float kRescaleThreshold = 8.0f;         // log2 units; below it O keeps its stale scale
 constexpr int kGatherThreadsDecode = 256;         // sparse decode: 8 gather warps
-constexpr int kGatherThreadsPrefill = 64;         // sparse prefill: 2 gather warps per stage
+constexpr int kGatherThreadsPrefill = 256;        // sparse prefill: 8 gather warps
 }  // namespace dtc
 
 __device__ int g_decode_tc_status = 0;
@@ -172,10 +175,23 @@ __device__ __forceinline__ uint32_t compress_even_bits(uint32_t m) {
   return m;
 }
 
+// The 36 S = Q K^T instructions of one block in stage ST, as straight-line code whose descriptors are
+// a warp-uniform base plus an immediate.
+template <int ST>
+__device__ __forceinline__ void s_block(uint32_t tmem, uint64_t desc_q, uint64_t desc_k, uint32_t idesc) {
+  using namespace dtc;
+#pragma unroll
+  for (int c = 0; c < 9; ++c)
+#pragma unroll
+    for (int s = 0; s < 4; ++s)
+      tc::mma_ws_ss(tmem + TMEM_S + ST * 32, tc::desc_advance(desc_q, c * kChunkBytes + s * 32),
+                    tc::desc_advance(desc_k, ST * kTileBytes + c * kChunkBytes + s * 32), idesc, (c | s) ? 1u : 0u);
+}
+
 // grid: kDense (s_q*ceil(hq_per_hk/64), h_k, parts), 192 threads;
-//       kSparseDecode (ceil(h_q/64), s_q, parts), 448 threads; kSparsePrefill (h_q/64, s_q), 320 threads
+//       kSparseDecode (ceil(h_q/64), s_q, parts), 448 threads; kSparsePrefill (h_q/64, s_q), 448 threads
 template <int MODE>
-__global__ void __launch_bounds__(MODE == kDense ? 192 : (MODE == kSparseDecode ? 448 : 320), 1)
+__global__ void __launch_bounds__(MODE == kDense ? 192 : 448, 1)
 mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtensorMap tmap_q,
               const __grid_constant__ CUtensorMap tmap_kv) {
   using namespace dtc;
@@ -267,6 +283,7 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
 #pragma unroll
             for (int c = 0; c < 9; ++c)
               tc::tma_load_4d(sKV + st * kTileBytes + c * kChunkBytes, &tmap_kv, c * 64, tile.kh, 0, page, bar(KV_FULL0 + st));
+            FMLA_TRACE_AT(g, 1);
           }
         }
         ++req;
@@ -275,11 +292,10 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
   } else if (warp >= 6) {
     // ================================ gather producers (sparse modes) ==================
     if constexpr (MODE == kSparsePrefill) {
-      // warps 6,7 fill stage 0, warps 8,9 fill stage 1 (every other block each), so two blocks of
-      // loads are in flight.  A warp copies 32 rows; for each row the 32 lanes copy consecutive
-      // 16-byte chunks (chunks lane, lane+32 and, for 8 lanes, lane+64 of the 72): coalesced
-      // cp.async with a handful of address instructions per row.
-      const int grp = (warp - 6) >> 1, wg = (warp - 6) & 1;
+      // Eight gather warps, eight rows each, all on the same block.  For each row the 32 lanes copy
+      // consecutive 16-byte pieces (pieces lane, lane+32 and, for 8 lanes, lane+64 of the 72):
+      // coalesced cp.async with a handful of address instructions per row.
+      const int gw = warp - 6;
       const char* kv = reinterpret_cast<const char*>(P.sp.kv);
       const int64_t row_bytes = P.sp.kv_stride_s * 2;
       const uint32_t lane_base = static_cast<uint32_t>((lane >> 3) * kChunkBytes);
@@ -289,22 +305,22 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
       for (int wi = 0; wi < tile.n_work && alive; ++wi) {
         const Work r = get_work<MODE>(P, tile, wi);
         for (int blk = r.blk_lo; blk < r.blk_hi && alive; ++blk, ++g) {
-          if ((g & 1) != grp) continue;
-          int my_idx = __ldg(r.idx + blk * 64 + wg * 32 + lane);
+          const int st = g & 1;
+          int my_idx = __ldg(r.idx + blk * 64 + gw * 8 + (lane & 7));
           if (my_idx < 0 || my_idx >= P.sp.s_kv) my_idx = -1;
-          alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(KV_EMPTY0 + grp), ((g >> 1) & 1) ^ 1, status, 11));
+          alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(KV_EMPTY0 + st), ((g >> 1) & 1) ^ 1, status, 11));
           if (!alive) break;
-          if (lane == 0 && wg == 0) FMLA_TRACE_AT(g, 0);
-          const uint32_t bal = __ballot_sync(0xffffffffu, my_idx >= 0);
-          if (lane == 0) sValid[grp * 2 + wg] = bal;                     // tokens 32*wg .. of this block
-          const uint32_t stage = sKV + grp * kTileBytes + lane_base;
-#pragma unroll 4
-          for (int rr = 0; rr < 32; ++rr) {
+          if (lane == 0 && gw == 0) FMLA_TRACE_AT(g, 0);
+          const uint32_t bal = __ballot_sync(0xffffffffu, my_idx >= 0) & 0xffu;
+          if (lane == 0) reinterpret_cast<volatile uint8_t*>(sValid)[st * 8 + gw] = static_cast<uint8_t>(bal);   // tokens 8*gw ..
+          const uint32_t stage = sKV + st * kTileBytes + lane_base;
+#pragma unroll
+          for (int rr = 0; rr < 8; ++rr) {
             const int idx = __shfl_sync(0xffffffffu, my_idx, rr);
             const bool ok = idx >= 0;
-            const int row = wg * 32 + rr;
-            const char* src = kv + (ok ? (int64_t)idx * row_bytes : 0) + (ok ? lane * 16 : 0);
-            const uint32_t dst = stage + row * 128 + ((sw ^ (row & 7)) << 4);
+            const int row = gw * 8 + rr;                  // row & 7 == rr
+            const char* src = kv + (ok ? (int64_t)idx * row_bytes + lane * 16 : 0);
+            const uint32_t dst = stage + row * 128 + ((sw ^ rr) << 4);
             cp_async16(dst, src, ok);
             cp_async16(dst + 4 * kChunkBytes, src + (ok ? 512 : 0), ok);
             if (lane < 8) cp_async16(dst + 8 * kChunkBytes, src + (ok ? 1024 : 0), ok);
@@ -312,8 +328,8 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
           cp_async_commit();
           cp_async_wait<0>();
           tc::fence_proxy_async_smem();
-          tc::mbar_arrive(bar(KV_FULL0 + grp));
-          if (lane == 0 && wg == 0) FMLA_TRACE_AT(g, 1);
+          tc::mbar_arrive(bar(KV_FULL0 + st));
+          if (lane == 0 && gw == 0) FMLA_TRACE_AT(g, 1);
         }
       }
     } else if constexpr (MODE == kSparseDecode) {
@@ -412,20 +428,19 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
       if (tc::elect_one()) {
         // the stage index is resolved by a branch so that every descriptor below is a warp-uniform
         // base plus an immediate
-        if (st == 0) {
 #pragma unroll
-          for (int h = 0; h < 2; ++h)
+        for (int h = 0; h < 2; ++h) {
+          if (st == 0) {
 #pragma unroll
             for (int s = 0; s < 4; ++s)
               tc::mma_ws_ss(tmem + TMEM_O + h * 128, tc::desc_advance(desc_p, s * 32),
                             tc::desc_advance(desc_v, h * 4 * kChunkBytes + s * 2048), idesc_o, (first_of_request && s == 0) ? 0u : 1u);
-        } else {
-#pragma unroll
-          for (int h = 0; h < 2; ++h)
+          } else {
 #pragma unroll
             for (int s = 0; s < 4; ++s)
               tc::mma_ws_ss(tmem + TMEM_O + h * 128, tc::desc_advance(desc_p, s * 32),
                             tc::desc_advance(desc_v, kTileBytes + h * 4 * kChunkBytes + s * 2048), idesc_o, (first_of_request && s == 0) ? 0u : 1u);
+          }
         }
         tc::tc_commit(bar(KV_EMPTY0 + st));
         tc::tc_commit(bar(P_EMPTY));
@@ -433,73 +448,62 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
       }
       __syncwarp();
     };
-    auto issue_s = [&](int gi, int rows_valid, bool last_of_request) {
-      const int st = gi & 1;
-      if constexpr (MODE == kDense) {
-        // rows of the last page beyond the sequence may hold anything (NaN included): zero them so
-        // that 0 * garbage cannot reach O through P V
-        if (rows_valid < 64) {
-          unsigned char* stage = smem + KV_OFF + st * kTileBytes;
-          const int nrows = 64 - rows_valid;
-          for (int i = lane; i < nrows * 72; i += 32) {
-            const int row = rows_valid + i / 72, c16 = i % 72;
-            *reinterpret_cast<uint4*>(stage + (c16 >> 3) * kChunkBytes + row * 128 + (c16 & 7) * 16) = make_uint4(0, 0, 0, 0);
-          }
-          tc::fence_proxy_async_smem();
-          __syncwarp();
+    // rows of the last page beyond the sequence may hold anything (NaN included): zero them so
+    // that 0 * garbage cannot reach O through P V
+    auto zero_tail_rows = [&](int st, int rows_valid) {
+      if (rows_valid < 64) {
+        unsigned char* stage = smem + KV_OFF + st * kTileBytes;
+        const int nrows = 64 - rows_valid;
+        for (int i = lane; i < nrows * 72; i += 32) {
+          const int row = rows_valid + i / 72, c16 = i % 72;
+          *reinterpret_cast<uint4*>(stage + (c16 >> 3) * kChunkBytes + row * 128 + (c16 & 7) * 16) = make_uint4(0, 0, 0, 0);
         }
+        tc::fence_proxy_async_smem();
+        __syncwarp();
       }
-      tc::tc_fence_after();
-      if (lane == 0) FMLA_TRACE_AT(gi, 2);
-      if (tc::elect_one()) {
-        if (st == 0) {
-#pragma unroll
-          for (int c = 0; c < 9; ++c)
-#pragma unroll
-            for (int s = 0; s < 4; ++s)
-              tc::mma_ws_ss(tmem + TMEM_S, tc::desc_advance(desc_q, c * kChunkBytes + s * 32),
-                            tc::desc_advance(desc_k, c * kChunkBytes + s * 32), idesc_s, (c | s) ? 1u : 0u);
-        } else {
-#pragma unroll
-          for (int c = 0; c < 9; ++c)
-#pragma unroll
-            for (int s = 0; s < 4; ++s)
-              tc::mma_ws_ss(tmem + TMEM_S + 32, tc::desc_advance(desc_q, c * kChunkBytes + s * 32),
-                            tc::desc_advance(desc_k, kTileBytes + c * kChunkBytes + s * 32), idesc_s, (c | s) ? 1u : 0u);
-        }
-        tc::tc_commit(bar(S_FULL0 + st));
-        FMLA_TRACE_AT(gi, 3);
-        if (last_of_request) tc::tc_commit(bar(Q_EMPTY));
-      }
-      __syncwarp();
     };
-    // a poll whose outcome is taken from lane 0, so that the warp stays convergent
-    auto ready = [&](int b, uint32_t parity) { return __shfl_sync(0xffffffffu, tc::mbar_test_wait(bar(b), parity) ? 1 : 0, 0) != 0; };
     for (int wi = 0; wi < tile.n_work && alive; ++wi) {
       const Work r = get_work<MODE>(P, tile, wi);
       const int nblk = r.blk_hi - r.blk_lo;
       if (nblk == 0) continue;
       alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_FULL), req & 1, status, 5));
-      // S of block js and P V of block jp (jp <= js) are issued in whichever order their inputs
-      // become ready, P V first: it releases a cache stage, and the next load depends on that
+      // S of block js and P V of block jp < js are issued in whichever order their inputs become
+      // ready; P V goes first when both are possible: it releases a cache stage and the next load
+      // depends on that.  One poll reads all barriers of interest at once, one per lane, and a ballot
+      // shares the result:  lane 0 P_FULL(jp)   lane 1 O_EMPTY   lane 2 S_EMPTY(js)   lane 3 KV_FULL(js)
+      // The S instructions of a block are issued from one straight-line site per stage (splitting
+      // them into several separately issued groups more than doubled the time of S: the tensor
+      // pipe drains in every gap).
       int js = 0, jp = 0, idle = 0;
       while (jp < nblk && alive) {
+        const int gi = g + min(js, nblk - 1), st = gi & 1;
+        const uint32_t ph = (gi >> 1) & 1;
+        int pb = P_FULL;
+        uint32_t pp = (g + jp) & 1;
+        if (lane == 1) { pb = O_EMPTY; pp = (req & 1) ^ 1; }
+        if (lane == 2) { pb = S_EMPTY0 + st; pp = ph ^ 1; }
+        if (lane >= 3) { pb = KV_FULL0 + st; pp = ph; }
+        const bool hit = lane < 4 && tc::mbar_test_wait(bar(pb), pp);
+        const uint32_t m = __ballot_sync(0xffffffffu, hit);
         bool did = false;
-        if (jp < js) {
-          const int gi = g + jp;
-          if (ready(P_FULL, gi & 1) && (jp > 0 || ready(O_EMPTY, (req & 1) ^ 1))) {
-            issue_pv(gi, jp == 0);
-            ++jp;
-            did = true;
+        if (jp < js && (m & 1u) && (jp > 0 || (m & 2u))) {
+          issue_pv(g + jp, jp == 0);
+          ++jp;
+          did = true;
+        } else if (js < nblk && (m & 0xcu) == 0xcu) {
+          if constexpr (MODE == kDense) zero_tail_rows(st, r.seqlen - (r.blk_lo + js) * 64);
+          tc::tc_fence_after();
+          if (lane == 0) FMLA_TRACE_AT(gi, 2);
+          if (tc::elect_one()) {
+            if (st == 0) s_block<0>(tmem, desc_q, desc_k, idesc_s);
+            else s_block<1>(tmem, desc_q, desc_k, idesc_s);
+            tc::tc_commit(bar(S_FULL0 + st));
+            FMLA_TRACE_AT(gi, 3);
+            if (js == nblk - 1) tc::tc_commit(bar(Q_EMPTY));
           }
-        }
-        if (!did && js < nblk) {
-          const int gi = g + js, st = gi & 1;
-          if (ready(KV_FULL0 + st, (gi >> 1) & 1) && ready(S_EMPTY0 + st, ((gi >> 1) & 1) ^ 1)) {
-            issue_s(gi, r.seqlen - (r.blk_lo + js) * 64, js == nblk - 1);
-            ++js;
-            did = true;
-          }
+          __syncwarp();
+          ++js;
+          did = true;
         }
         if (did) {
           idle = 0;
@@ -507,7 +511,7 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
           if (lane == 0) atomicCAS(status, 0, 6);
           alive = false;
         } else {
-          __nanosleep(32);   // a tight poll would take issue slots from the softmax warp on this scheduler
+          __nanosleep(20);   // a tight poll would take issue slots from the softmax warp on this scheduler
         }
       }
       g += nblk;
@@ -744,7 +748,7 @@ static cudaError_t launch_tc(const TcParams& P, const CUtensorMap& tq, const CUt
   auto kern = mla_tc_kernel<MODE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dtc::SMEM_BYTES);
   if (e != cudaSuccess) return e;
-  kern<<<grid, MODE == kDense ? 192 : (MODE == kSparseDecode ? 448 : 320), dtc::SMEM_BYTES, stream>>>(P, tq, tkv);
+  kern<<<grid, MODE == kDense ? 192 : 448, dtc::SMEM_BYTES, stream>>>(P, tq, tkv);
   return cudaGetLastError();
 }
 
