@@ -288,7 +288,7 @@ class DenseFwdBwd:
     """BASELINE config 5a: dense causal varlen MHA forward + backward, h 128, d 192/128, 8 sequences U[1024,8192]."""
     metric, unit, dtype = "dense_mha_varlen_fwd_bwd_tflops", "TFLOP/s", "bf16"
     bound = "tensor"
-    kernel_name = "dense_fwd_kernel + dense_bwd_*"
+    kernel_name = "dense_fwd_tc_kernel<192> + dense_bwd_*"
     launches_per_step = 4
 
     def __init__(self, nseq: int = 8, h: int = 128):
@@ -329,7 +329,26 @@ class DenseFwdBwd:
         return out, lse
 
 
+class DenseFwd(DenseFwdBwd):
+    """BASELINE config 5a, forward only (the reference quotes forward and backward separately)."""
+    metric = "dense_mha_varlen_fwd_tflops"
+    kernel_name = "dense_fwd_tc_kernel<192>"
+    launches_per_step = 1
+
+    def __init__(self, nseq: int = 8, h: int = 128):
+        super().__init__(nseq, h)
+        self.name = f"dense_mha_varlen fwd {nseq} seqs/gpu L~U[1024,8192] h={h} d=192/128 causal"
+
+    def alg_flops(self):
+        return int(self.pairs * self.h * 2 * (192 + 128))
+
+    def step(self, events=None):
+        with torch.no_grad():
+            return self.fm.flash_attn_varlen_func(self.q, self.k, self.v, self.cu, self.cu, self.max_len, self.max_len, causal=True)
+
+
 WORKLOADS = {
+    "dense_fwd": lambda: DenseFwd(),
     "dense_decode": lambda: DenseDecode(1),
     "dense_decode_sq2": lambda: DenseDecode(2),
     "sparse_decode": lambda: SparseDecode(),

@@ -102,6 +102,9 @@ cudaError_t launch_merge_peer_partials(const float* lse_accum, const float* o_ac
 cudaError_t read_merge_status(int* host_status, bool reset);
 cudaError_t launch_sparse_prefill_mma(const SparsePrefillKernelParams& p, cudaStream_t stream);
 cudaError_t launch_dense_fwd_mma(const DenseKernelParams& p, cudaStream_t stream);
+// tcgen05 / TMA / TMEM forward (dense_fwd_tc.cu) and its status word
+cudaError_t launch_dense_fwd_tc(const DenseKernelParams& p, cudaStream_t stream);
+cudaError_t read_dense_tc_status(int* host_status, bool reset);
 cudaError_t launch_dense_bwd_mma(const DenseKernelParams& p, cudaStream_t stream);
 cudaError_t launch_quantize_kv_fp8(const void* kv, int64_t kv_stride_row, int num_tokens, const int* dst_slots,
                                    void* cache, int64_t cache_stride_slot, cudaStream_t stream);

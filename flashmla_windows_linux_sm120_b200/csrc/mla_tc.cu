@@ -248,6 +248,11 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
       if constexpr (MODE == kDense) tc::prefetch_tensormap(&tmap_kv);
       int g = 0, req = 0;
       bool alive = true;
+#ifdef FMLA_STAGGER_NS
+      if constexpr (MODE == kDense) {
+        if (blockIdx.z & 1) { const long long t0 = clock64(); while (clock64() - t0 < FMLA_STAGGER_NS) {} }
+      }
+#endif
       for (int wi = 0; wi < tile.n_work && alive; ++wi) {
         const Work r = get_work<MODE>(P, tile, wi);
         if (r.blk_hi == r.blk_lo) continue;
