@@ -343,7 +343,7 @@ int fmla_dense_prefill_bwd(const fmla_dense_params* P, void* stream) {
   if (rc) return rc;
   rc = require_blackwell();
   if (rc) return rc;
-  cudaError_t e = fmla::launch_dense_bwd_mma(k, static_cast<cudaStream_t>(stream));
+  cudaError_t e = fmla::launch_dense_bwd_tc(k, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? FMLA_OK : cuda_fail(e, "dense backward launch");
 }
 
@@ -357,6 +357,9 @@ int fmla_device_status(int* status_host, int reset) {
   if (*status_host == 0) *status_host = merge_status;
   int dense_status = 0;
   e = fmla::read_dense_tc_status(&dense_status, reset != 0);
+  if (e != cudaSuccess) return cuda_fail(e, "reading the device status word");
+  if (*status_host == 0) *status_host = dense_status;
+  e = fmla::read_dense_bwd_tc_status(&dense_status, reset != 0);
   if (e != cudaSuccess) return cuda_fail(e, "reading the device status word");
   if (*status_host == 0) *status_host = dense_status;
   return *status_host == 0 ? FMLA_OK : fail(FMLA_ERR_DEVICE_TIMEOUT, "a bounded device-side wait expired (code %d)", *status_host);

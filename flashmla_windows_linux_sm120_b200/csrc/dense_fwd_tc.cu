@@ -23,8 +23,7 @@
 // CTA drain and free its tensor memory.
 #include "kernels.h"
 #include "tc_common.cuh"
-
-#include <cuda.h>
+#include "tma_host.cuh"
 
 namespace fmla {
 
@@ -327,32 +326,6 @@ dense_fwd_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid_co
 }
 
 // ---- host side ----------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn dense_encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void* f = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess) f = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(f);
-  }();
-  return fn;
-}
-
-// bf16 tensor [tokens][heads][d] with element strides (stride_t, stride_h, 1); box = 128 tokens x 64 columns of one head
-static bool make_map_thd(CUtensorMap* m, const void* base, int d, int heads, int tokens, int64_t stride_h, int64_t stride_t) {
-  EncodeTiledFn enc = dense_encode_fn();
-  if (!enc) return false;
-  cuuint64_t dims[3] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(tokens)};
-  cuuint64_t strides[2] = {static_cast<cuuint64_t>(stride_h) * 2, static_cast<cuuint64_t>(stride_t) * 2};
-  cuuint32_t box[3] = {64, 1, 128};
-  cuuint32_t estr[3] = {1, 1, 1};
-  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int D_QK>
 static cudaError_t launch_fwd_tc(const DenseKernelParams& p, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                                  cudaStream_t stream) {
@@ -367,9 +340,9 @@ static cudaError_t launch_fwd_tc(const DenseKernelParams& p, const CUtensorMap& 
 
 cudaError_t launch_dense_fwd_tc(const DenseKernelParams& p, cudaStream_t stream) {
   CUtensorMap tq, tk, tv;
-  if (!make_map_thd(&tq, p.q, p.d_qk, p.h_q, p.total_q, p.q_stride_h, p.q_stride_t)) return cudaErrorInvalidValue;
-  if (!make_map_thd(&tk, p.k, p.d_qk, p.h_k, p.total_k, p.k_stride_h, p.k_stride_t)) return cudaErrorInvalidValue;
-  if (!make_map_thd(&tv, p.v, p.d_v, p.h_k, p.total_k, p.v_stride_h, p.v_stride_t)) return cudaErrorInvalidValue;
+  if (!tmah::make_map_thd(&tq, p.q, p.d_qk, p.h_q, p.total_q, p.q_stride_h, p.q_stride_t, 128)) return cudaErrorInvalidValue;
+  if (!tmah::make_map_thd(&tk, p.k, p.d_qk, p.h_k, p.total_k, p.k_stride_h, p.k_stride_t, 128)) return cudaErrorInvalidValue;
+  if (!tmah::make_map_thd(&tv, p.v, p.d_v, p.h_k, p.total_k, p.v_stride_h, p.v_stride_t, 128)) return cudaErrorInvalidValue;
   if (p.d_qk == 192) return launch_fwd_tc<192>(p, tq, tk, tv, stream);
   return launch_fwd_tc<128>(p, tq, tk, tv, stream);
 }

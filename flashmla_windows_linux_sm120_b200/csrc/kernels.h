@@ -105,6 +105,9 @@ cudaError_t launch_dense_fwd_mma(const DenseKernelParams& p, cudaStream_t stream
 // tcgen05 / TMA / TMEM forward (dense_fwd_tc.cu) and its status word
 cudaError_t launch_dense_fwd_tc(const DenseKernelParams& p, cudaStream_t stream);
 cudaError_t read_dense_tc_status(int* host_status, bool reset);
+// tcgen05 / TMA / TMEM backward (dense_bwd_tc.cu) and its status word
+cudaError_t launch_dense_bwd_tc(const DenseKernelParams& p, cudaStream_t stream);
+cudaError_t read_dense_bwd_tc_status(int* host_status, bool reset);
 cudaError_t launch_dense_bwd_mma(const DenseKernelParams& p, cudaStream_t stream);
 cudaError_t launch_quantize_kv_fp8(const void* kv, int64_t kv_stride_row, int num_tokens, const int* dst_slots,
                                    void* cache, int64_t cache_stride_slot, cudaStream_t stream);
