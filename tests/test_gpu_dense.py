@@ -44,6 +44,44 @@ def test_dense_fwd_bwd(d, dv, causal, varlen):
 
 
 @pytest.mark.parametrize("d", [192, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_dense_fwd_bwd_long(d, causal):
+    """Sequences of several 128-row tiles and key blocks (the rings wrap and every barrier changes phase),
+    with more keys than queries so that the causal mask is bottom-right aligned."""
+    c = gen.make_dense_case(gen.DenseCase(b=2, mean_sq=520, mean_sk=760, varlen=True, h=2, h_k=2, d=d, dv=128, causal=causal))
+    out, lse, (dq, dk, dvv) = _run(c, causal, True)
+    r_out, r_lse, r_dq, r_dk, r_dv = dense.dense_fwd_bwd_ref(c["q"], c["k"], c["v"], c["d_out"], c["cu_q"], c["cu_k"],
+                                                             causal, c["scale"])
+    assert check_is_allclose("out", out, r_out, **TOL)
+    assert check_is_allclose("lse", lse, r_lse, **LSE_TOL)
+    assert check_is_allclose("dq", dq, r_dq, **TOL)
+    assert check_is_allclose("dk", dk, r_dk, **TOL)
+    assert check_is_allclose("dv", dvv, r_dv, **TOL)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_dense_neighbour_sequence_does_not_leak(causal):
+    """A tile that overhangs the end of its sequence reads rows of the next one.  Non-finite values there
+    must not reach this sequence's outputs: the result equals the one computed for the sequence alone."""
+    c = gen.make_dense_case(gen.DenseCase(b=2, mean_sq=200, mean_sk=200, varlen=True, h=2, h_k=2, d=192, dv=128, causal=causal))
+    cu_q, cu_k = c["cu_q"], c["cu_k"]
+    lq0, lk0 = int(cu_q[1]), int(cu_k[1])
+    assert lq0 % 64 and lk0 % 64, "the case must leave partial tiles"
+    both = {n: c[n].clone() for n in ("q", "k", "v", "d_out")}
+    both["q"][lq0:] = float("nan")
+    both["d_out"][lq0:] = float("inf")
+    both["k"][lk0:] = float("nan")
+    both["v"][lk0:] = float("inf")
+    poisoned = dict(c, **both)
+    out, lse, (dq, dk, dvv) = _run(poisoned, causal, True)
+    alone = dict(c, q=c["q"][:lq0], k=c["k"][:lk0], v=c["v"][:lk0], d_out=c["d_out"][:lq0], cu_q=cu_q[:2], cu_k=cu_k[:2],
+                 max_q=lq0, max_k=lk0)
+    a_out, a_lse, (a_dq, a_dk, a_dv) = _run(alone, causal, True)
+    assert torch.equal(out[:lq0], a_out) and torch.equal(lse[:lq0], a_lse)
+    assert torch.equal(dq[:lq0], a_dq) and torch.equal(dk[:lk0], a_dk) and torch.equal(dvv[:lk0], a_dv)
+
+
+@pytest.mark.parametrize("d", [192, 128])
 def test_dense_fwd_gqa(d):
     c = gen.make_dense_case(gen.DenseCase(b=2, mean_sq=150, mean_sk=260, varlen=True, h=8, h_k=2, d=d, dv=128, causal=True))
     out, lse, _ = _run(c, True, False)
