@@ -199,9 +199,7 @@ static int decode_impl(const fmla_decode_params* P, const fmla_peer_push* push, 
     e = cudaEventRecord(static_cast<cudaEvent_t>(a.profile_event_begin), s);
     if (e != cudaSuccess) return cuda_fail(e, "cudaEventRecord");
   }
-  static const bool use_mma = [] { const char* v = getenv("FMLA_USE_MMA_SYNC"); return v && v[0] == '1'; }();   // A/B timing only
-  if (use_mma) e = fmla::launch_decode_mma(k, s);
-  else e = sparse ? fmla::launch_decode_sparse_tc(k, s) : fmla::launch_decode_dense_tc(k, s);
+  e = sparse ? fmla::launch_decode_sparse_tc(k, s) : fmla::launch_decode_dense_tc(k, s);
   if (e != cudaSuccess) return cuda_fail(e, "decode attention launch");
   if (a.profile_event_end) {
     e = cudaEventRecord(static_cast<cudaEvent_t>(a.profile_event_end), s);
@@ -273,9 +271,7 @@ int fmla_sparse_prefill_fwd(const fmla_sparse_prefill_params* P, void* stream) {
   k.kv = a.kv; k.kv_stride_s = a.kv_stride_s;
   k.indices = a.indices; k.indices_stride_s = a.indices_stride_s;
   k.out = a.out; k.max_logits = a.max_logits; k.lse = a.lse;
-  static const bool use_mma = [] { const char* v = getenv("FMLA_USE_MMA_SYNC"); return v && v[0] == '1'; }();   // A/B timing only
-  cudaError_t e = use_mma ? fmla::launch_sparse_prefill_mma(k, static_cast<cudaStream_t>(stream))
-                          : fmla::launch_sparse_prefill_tc(k, static_cast<cudaStream_t>(stream));
+  cudaError_t e = fmla::launch_sparse_prefill_tc(k, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? FMLA_OK : cuda_fail(e, "sparse prefill launch");
 }
 

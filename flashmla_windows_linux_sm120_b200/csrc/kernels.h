@@ -81,7 +81,6 @@ int set_error(int code, const char* message);
 
 cudaError_t launch_get_mla_metadata(const int* seqlens_k, int batch, int num_sm_parts, int topk, int* md,
                                     int* num_splits, cudaStream_t stream);
-cudaError_t launch_decode_mma(const DecodeKernelParams& p, cudaStream_t stream);
 // tcgen05 / TMA / TMEM kernels (mla_tc.cu): dense decode, sparse FP8 decode, sparse prefill
 cudaError_t launch_decode_dense_tc(const DecodeKernelParams& p, cudaStream_t stream);
 cudaError_t launch_decode_sparse_tc(const DecodeKernelParams& p, cudaStream_t stream);
@@ -100,15 +99,12 @@ cudaError_t launch_merge_peer_partials(const float* lse_accum, const float* o_ac
                                        int64_t o_stride_row, float* lse, const unsigned int* flags, unsigned int epoch,
                                        int max_polls, cudaStream_t stream);
 cudaError_t read_merge_status(int* host_status, bool reset);
-cudaError_t launch_sparse_prefill_mma(const SparsePrefillKernelParams& p, cudaStream_t stream);
-cudaError_t launch_dense_fwd_mma(const DenseKernelParams& p, cudaStream_t stream);
 // tcgen05 / TMA / TMEM forward (dense_fwd_tc.cu) and its status word
 cudaError_t launch_dense_fwd_tc(const DenseKernelParams& p, cudaStream_t stream);
 cudaError_t read_dense_tc_status(int* host_status, bool reset);
 // tcgen05 / TMA / TMEM backward (dense_bwd_tc.cu) and its status word
 cudaError_t launch_dense_bwd_tc(const DenseKernelParams& p, cudaStream_t stream);
 cudaError_t read_dense_bwd_tc_status(int* host_status, bool reset);
-cudaError_t launch_dense_bwd_mma(const DenseKernelParams& p, cudaStream_t stream);
 cudaError_t launch_quantize_kv_fp8(const void* kv, int64_t kv_stride_row, int num_tokens, const int* dst_slots,
                                    void* cache, int64_t cache_stride_slot, cudaStream_t stream);
 
