@@ -32,8 +32,8 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 # dram__bytes_read + dram__bytes_write per launch of the dominant kernel, from the committed ncu capture
-# (profiles/decode_dense_tc_kernel__dense_decode_b128_sq1.md)
-TRAFFIC_BYTES = {"dense_decode": 709.4e6}
+# (profiles/mla_tc_kernel_dense__dense_decode_b128_sq1.md)
+TRAFFIC_BYTES = {"dense_decode": 708.7e6}
 
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
