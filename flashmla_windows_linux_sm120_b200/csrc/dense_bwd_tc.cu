@@ -29,6 +29,16 @@ namespace fmla {
 namespace dbt {
 constexpr int kResChunk = 128 * 128;              // resident tiles: [128 rows x 64 bf16] chunks
 constexpr int kStgChunk = 64 * 128;               // streamed tiles: [64 rows x 64 bf16] chunks
+constexpr int kStages = 3;                        // ring of streamed tiles (the TMEM buffers alternate independently)
+template <int V> struct IC { static constexpr int value = V; };
+// calls f(IC<stage>, IC<buffer>) with compile-time stage (0..2) and buffer (0..1): every combination gets
+// its own straight-line code, so that all descriptors stay a warp-uniform base plus an immediate
+template <typename F>
+__device__ __forceinline__ void dispatch_stage_buffer(int st, int b, F&& f) {
+  if (st == 0) { if (b == 0) f(IC<0>{}, IC<0>{}); else f(IC<0>{}, IC<1>{}); }
+  else if (st == 1) { if (b == 0) f(IC<1>{}, IC<0>{}); else f(IC<1>{}, IC<1>{}); }
+  else { if (b == 0) f(IC<2>{}, IC<0>{}); else f(IC<2>{}, IC<1>{}); }
+}
 template <int D_QK>
 struct Layout {
   static constexpr int NCH = D_QK / 64;
@@ -39,7 +49,7 @@ struct Layout {
   static constexpr int kStage = kStgA + kStgB;
   static constexpr int RES_OFF = 0;
   static constexpr int STG_OFF = kResA + kResB;
-  static constexpr int BAR_OFF = STG_OFF + 2 * kStage;
+  static constexpr int BAR_OFF = STG_OFF + kStages * kStage;
   static constexpr int VEC_OFF = BAR_OFF + 128;   // float [2][2][64]: per-query lse*log2(e) and delta (dK/dV kernel)
   static constexpr int MISC_OFF = VEC_OFF + 1024;
   static constexpr int SMEM_BYTES = MISC_OFF + 16;
@@ -102,7 +112,7 @@ __device__ __forceinline__ void mma_tmem_stg(uint32_t d_tmem, uint32_t a_tmem, u
 // Per step (64 keys): S = Q K^T and dP = dO V^T into one of two TMEM buffer pairs, dS over S, then
 // dQ += dS K.  TMEM: dQ = [0, D_QK), buffer b: S = [192 + 128 b, +64), dP = [256 + 128 b, +64).
 namespace dbt {
-enum BarQ { Q_RES_FULL = 0, Q_KV_FULL0, Q_KV_FULL1, Q_KV_EMPTY0, Q_KV_EMPTY1, Q_SD_FULL0, Q_SD_FULL1, Q_DS_FULL0, Q_DS_FULL1, Q_DONE, Q_NUM_BARS };
+enum BarQ { Q_RES_FULL = 0, Q_KV_FULL0, Q_KV_EMPTY0 = Q_KV_FULL0 + kStages, Q_SD_FULL0 = Q_KV_EMPTY0 + kStages, Q_SD_FULL1, Q_DS_FULL0, Q_DS_FULL1, Q_DONE, Q_NUM_BARS };
 }
 
 template <int D_QK>
@@ -156,10 +166,10 @@ dense_bwd_dq_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid
       for (int c = 0; c < 2; ++c) tc::tma_load_3d(sDO + c * kResChunk, &tmap_do, c * 64, head, q0 + m_base, bar(Q_RES_FULL));
       bool alive = true;
       for (int j = 0; j < nblk && alive; ++j) {
-        const int st = j & 1;
+        const int st = j % kStages;
         const uint32_t stage = sStg + st * L::kStage;
         const int tok = k0 + j * 64;
-        alive = tc::mbar_wait(bar(Q_KV_EMPTY0 + st), ((j >> 1) & 1) ^ 1, status, 51);
+        alive = tc::mbar_wait(bar(Q_KV_EMPTY0 + st), ((j / kStages) & 1) ^ 1, status, 51);
         if (!alive) break;
         tc::mbar_arrive_expect_tx(bar(Q_KV_FULL0 + st), L::kStage);
 #pragma unroll
@@ -180,33 +190,35 @@ dense_bwd_dq_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid
     bool alive = nblk > 0;
     if (alive) alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_RES_FULL), 0, status, 52));
     auto issue_dq = [&](int j) {
-      const int st = j & 1;
-      alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_DS_FULL0 + st), (j >> 1) & 1, status, 53));
+      const int st = j % kStages, bf = j & 1;
+      alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_DS_FULL0 + bf), (j >> 1) & 1, status, 53));
       if (!alive) return;
       tc::tc_fence_after();
       if (tc::elect_one()) {
-        if (st == 0) mma_tmem_stg(tmem + TM_DQ, tmem + TM_SD, desc_kt, idesc_dq, j == 0);
-        else mma_tmem_stg(tmem + TM_DQ, tmem + TM_SD + 128, tc::desc_advance(desc_kt, L::kStage), idesc_dq, j == 0);
+        dispatch_stage_buffer(st, bf, [&](auto ST, auto BF) {
+          mma_tmem_stg(tmem + TM_DQ, tmem + TM_SD + decltype(BF)::value * 128, tc::desc_advance(desc_kt, decltype(ST)::value * L::kStage),
+                       idesc_dq, j == 0);
+        });
         tc::tc_commit(bar(Q_KV_EMPTY0 + st));
       }
       __syncwarp();
     };
     for (int j = 0; j < nblk && alive; ++j) {
-      const int st = j & 1;
-      alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_KV_FULL0 + st), (j >> 1) & 1, status, 54));
+      const int st = j % kStages, bf = j & 1;
+      alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_KV_FULL0 + st), (j / kStages) & 1, status, 54));
       if (!alive) break;
       // K rows past the end of the sequence must be exact zeros for dQ += dS K
       if (lk - j * 64 < 64) zero_stage_tail(smem + L::STG_OFF + st * L::kStage, L::NCH, lk - j * 64, lane);
       tc::tc_fence_after();
       if (tc::elect_one()) {
-        if (st == 0) {
-          mma_res_stg<L::NCH>(tmem + TM_SD, desc_q, desc_k, idesc_sd);
-          mma_res_stg<2>(tmem + TM_SD + 64, desc_do, desc_v, idesc_sd);
-        } else {
-          mma_res_stg<L::NCH>(tmem + TM_SD + 128, desc_q, tc::desc_advance(desc_k, L::kStage), idesc_sd);
-          mma_res_stg<2>(tmem + TM_SD + 192, desc_do, tc::desc_advance(desc_v, L::kStage), idesc_sd);
-        }
-        tc::tc_commit(bar(Q_SD_FULL0 + st));
+        // the S / dP buffer pair bf was last read (as dS) by the dQ instructions of step j-2, issued earlier
+        // by this thread: the tensor pipe runs them in order
+        dispatch_stage_buffer(st, bf, [&](auto ST, auto BF) {
+          constexpr int kOff = decltype(ST)::value * L::kStage, kCol = TM_SD + decltype(BF)::value * 128;
+          mma_res_stg<L::NCH>(tmem + kCol, desc_q, tc::desc_advance(desc_k, kOff), idesc_sd);
+          mma_res_stg<2>(tmem + kCol + 64, desc_do, tc::desc_advance(desc_v, kOff), idesc_sd);
+        });
+        tc::tc_commit(bar(Q_SD_FULL0 + bf));
       }
       __syncwarp();
       if (j > 0) issue_dq(j - 1);
@@ -297,7 +309,7 @@ dense_bwd_dq_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid
 // then dV += P^T dO and dK += dS^T Q.
 // TMEM: dV = [0,128), dK = [128, 128 + D_QK), S^T buffer b = [320 + 64 b, +64), dP^T = [448, 512).
 namespace dbt {
-enum BarK { K_RES_FULL = 0, K_QD_FULL0, K_QD_FULL1, K_QD_EMPTY0, K_QD_EMPTY1, K_SD_FULL, K_PD_FULL, K_DONE, K_NUM_BARS };
+enum BarK { K_RES_FULL = 0, K_QD_FULL0, K_QD_EMPTY0 = K_QD_FULL0 + kStages, K_SD_FULL = K_QD_EMPTY0 + kStages, K_PD_FULL, K_DONE, K_NUM_BARS };
 }
 
 template <int D_QK>
@@ -353,10 +365,10 @@ dense_bwd_dkdv_tc_kernel(const __grid_constant__ DenseKernelParams p, const __gr
       for (int c = 0; c < 2; ++c) tc::tma_load_3d(sV + c * kResChunk, &tmap_v, c * 64, head, k0 + n_base, bar(K_RES_FULL));
       bool alive = true;
       for (int j = 0; j < nstep && alive; ++j) {
-        const int st = j & 1;
+        const int st = j % kStages;
         const uint32_t stage = sStg + st * L::kStage;
         const int tok = q0 + (jb_lo + j) * 64;
-        alive = tc::mbar_wait(bar(K_QD_EMPTY0 + st), ((j >> 1) & 1) ^ 1, status, 61);
+        alive = tc::mbar_wait(bar(K_QD_EMPTY0 + st), ((j / kStages) & 1) ^ 1, status, 61);
         if (!alive) break;
         tc::mbar_arrive_expect_tx(bar(K_QD_FULL0 + st), L::kStage);
 #pragma unroll
@@ -380,23 +392,25 @@ dense_bwd_dkdv_tc_kernel(const __grid_constant__ DenseKernelParams p, const __gr
     if (alive) alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(K_RES_FULL), 0, status, 62));
     // waits for the tile of step j, clears its rows past the end of the sequence, issues S^T(j)
     auto issue_st = [&](int j) {
-      const int st = j & 1;
-      alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(K_QD_FULL0 + st), (j >> 1) & 1, status, 63));
+      const int st = j % kStages, bf = j & 1;
+      alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(K_QD_FULL0 + st), (j / kStages) & 1, status, 63));
       if (!alive) return;
       const int rows_valid = lq - (jb_lo + j) * 64;
       if (rows_valid < 64) zero_stage_tail(smem + L::STG_OFF + st * L::kStage, L::NCH + 2, rows_valid, lane);
       tc::tc_fence_after();
       if (tc::elect_one()) {
-        if (st == 0) mma_res_stg<L::NCH>(tmem + TM_ST, desc_k, desc_q, idesc_sd);
-        else mma_res_stg<L::NCH>(tmem + TM_ST + 64, desc_k, tc::desc_advance(desc_q, L::kStage), idesc_sd);
+        dispatch_stage_buffer(st, bf, [&](auto ST, auto BF) {
+          mma_res_stg<L::NCH>(tmem + TM_ST + decltype(BF)::value * 64, desc_k, tc::desc_advance(desc_q, decltype(ST)::value * L::kStage), idesc_sd);
+        });
       }
       __syncwarp();
     };
     auto issue_dpt = [&](int j) {
-      const int st = j & 1;
+      const int st = j % kStages;
       if (tc::elect_one()) {
-        if (st == 0) mma_res_stg<2>(tmem + TM_DPT, desc_v, desc_do, idesc_sd);
-        else mma_res_stg<2>(tmem + TM_DPT, desc_v, tc::desc_advance(desc_do, L::kStage), idesc_sd);
+        dispatch_stage_buffer(st, 0, [&](auto ST, auto) {
+          mma_res_stg<2>(tmem + TM_DPT, desc_v, tc::desc_advance(desc_do, decltype(ST)::value * L::kStage), idesc_sd);
+        });
         tc::tc_commit(bar(K_SD_FULL));
       }
       __syncwarp();
@@ -404,28 +418,25 @@ dense_bwd_dkdv_tc_kernel(const __grid_constant__ DenseKernelParams p, const __gr
     if (alive) issue_st(0);
     if (alive) issue_dpt(0);
     for (int j = 0; j < nstep && alive; ++j) {
-      const int st = j & 1;
+      const int st = j % kStages, bf = j & 1;
       if (j + 1 < nstep) issue_st(j + 1);
       if (alive) alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(K_PD_FULL), j & 1, status, 64));
       if (!alive) break;
       tc::tc_fence_after();
       if (tc::elect_one()) {
-        if (st == 0) {
-          mma_tmem_stg(tmem + TM_DV, tmem + TM_ST, desc_dot, idesc_dv, j == 0);
-          mma_tmem_stg(tmem + TM_DK, tmem + TM_DPT, desc_qt, idesc_dk, j == 0);
-        } else {
-          mma_tmem_stg(tmem + TM_DV, tmem + TM_ST + 64, tc::desc_advance(desc_dot, L::kStage), idesc_dv, j == 0);
-          mma_tmem_stg(tmem + TM_DK, tmem + TM_DPT, tc::desc_advance(desc_qt, L::kStage), idesc_dk, j == 0);
-        }
+        dispatch_stage_buffer(st, bf, [&](auto ST, auto BF) {
+          constexpr int kOff = decltype(ST)::value * L::kStage;
+          mma_tmem_stg(tmem + TM_DV, tmem + TM_ST + decltype(BF)::value * 64, tc::desc_advance(desc_dot, kOff), idesc_dv, j == 0);
+          mma_tmem_stg(tmem + TM_DK, tmem + TM_DPT, tc::desc_advance(desc_qt, kOff), idesc_dk, j == 0);
+        });
         if (j + 1 >= nstep) tc::tc_commit(bar(K_DONE));
       }
       __syncwarp();
       // dP^T of the next step goes into the buffer that the dK instructions above read (the tensor
-      // pipe runs them in order); only after it may the stage of step j be refilled, because the
-      // commit covers everything issued so far
-      if (j + 1 < nstep) issue_dpt(j + 1);
+      // pipe runs them in order); the stage of step j is handed back right after its last readers
       if (tc::elect_one()) tc::tc_commit(bar(K_QD_EMPTY0 + st));
       __syncwarp();
+      if (j + 1 < nstep) issue_dpt(j + 1);
     }
   } else {
     // ================================ element-wise / epilogue ==========================
