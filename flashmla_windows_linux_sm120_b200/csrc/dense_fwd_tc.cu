@@ -2,9 +2,9 @@
 // tcgen05 / TMA / tensor memory.
 //
 // One CTA = 128 query rows of one (sequence, head); keys are walked in blocks of 128.
-//   warps 0-3 softmax : one thread per query row (TMEM lane = row): S -> registers, mask, running
-//                       max / sum (base 2), P (bf16) written back into the columns S came from,
-//                       lazy rescale of O, final 1/l normalisation and stores
+//   warps 0-3, 6-9 softmax : two threads per query row (TMEM lane = row, 64 key columns each):
+//                       S -> registers, mask, running max / sum (base 2), P (bf16) written back into
+//                       the columns S came from, lazy rescale of O, final 1/l normalisation and stores
 //   warp 4   TMA      : Q tile once; K and V blocks into a 2-stage ring (64-column chunks of
 //                       [128 rows x 128 bytes], 128-byte swizzle), K and V with barriers of their own
 //                       so that K is refilled right after S and V right after P V
@@ -41,7 +41,8 @@ struct Layout {
   static constexpr int Q_OFF = 0;
   static constexpr int KV_OFF = kQBytes;
   static constexpr int BAR_OFF = KV_OFF + 2 * kStageBytes;
-  static constexpr int MISC_OFF = BAR_OFF + 128;
+  static constexpr int XCH_OFF = BAR_OFF + 128;    // float [2][256]: row maxima / sums exchanged between the two threads of a row
+  static constexpr int MISC_OFF = XCH_OFF + 2048;
   static constexpr int SMEM_BYTES = MISC_OFF + 16;
   static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory limit per CTA");
 };
@@ -49,6 +50,17 @@ static_assert(NUM_BARS * 8 <= 128, "barrier area too small");
 }  // namespace dft
 
 __device__ int g_dense_tc_status = 0;
+
+// Optional timeline of the first blocks of CTA (0,0,0), compiled in with -DFMLA_TRACE only.
+#ifdef FMLA_TRACE
+__device__ long long g_dense_trace[64 * 16];
+#define DFT_TRACE_AT(blk, slot)                                                          \
+  do {                                                                                     \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (blk) < 64) g_dense_trace[(blk) * 16 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define DFT_TRACE_AT(blk, slot) do {} while (0)
+#endif
 
 // The S = Q K^T instructions of one key block in stage ST (result into S buffer ST), as straight-line
 // code whose descriptors are a warp-uniform base plus an immediate.
@@ -72,9 +84,9 @@ __device__ __forceinline__ void dense_pv_block(uint32_t tmem, uint64_t desc_v, u
                (first && s == 0) ? 0u : 1u);
 }
 
-// grid (ceil(max_seqlen_q/128), h_q, batch), 192 threads
+// grid (ceil(max_seqlen_q/128), h_q, batch), 320 threads
 template <int D_QK>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 dense_fwd_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid_constant__ CUtensorMap tmap_q,
                     const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v) {
   using namespace dft;
@@ -84,6 +96,8 @@ dense_fwd_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid_co
   const uint32_t sQ = sbase + L::Q_OFF, sKV = sbase + L::KV_OFF;
   auto bar = [&](int i) { return sbase + L::BAR_OFF + i * 8; };
   volatile uint32_t* sTmem = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFF);
+  volatile int* sAbort = reinterpret_cast<volatile int*>(smem + L::MISC_OFF + 8);   // set by a softmax thread whose wait expired
+  float* sXch = reinterpret_cast<float*>(smem + L::XCH_OFF);
   int* status = &g_dense_tc_status;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -106,10 +120,11 @@ dense_fwd_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid_co
   if (tid == 0) {
     tc::mbar_init(bar(Q_FULL), 1);
     for (int i = K_FULL0; i <= S_FULL1; ++i) tc::mbar_init(bar(i), 1);
-    tc::mbar_init(bar(P_FULL0), 128);
-    tc::mbar_init(bar(P_FULL1), 128);
+    tc::mbar_init(bar(P_FULL0), 256);
+    tc::mbar_init(bar(P_FULL1), 256);
     tc::mbar_init(bar(PV_DONE), 1);
     tc::fence_mbar_init();
+    *sAbort = 0;
   }
   if (warp == 5) tc::tmem_alloc(sbase + L::MISC_OFF, 512);
   tc::tc_fence_before();
@@ -134,11 +149,13 @@ dense_fwd_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid_co
         const int tok = k0 + j * 128;
         alive = tc::mbar_wait(bar(K_EMPTY0 + st), ph, status, 41);
         if (!alive) break;
+        DFT_TRACE_AT(j, 0);
         tc::mbar_arrive_expect_tx(bar(K_FULL0 + st), L::kQBytes);
 #pragma unroll
         for (int c = 0; c < L::NCH; ++c) tc::tma_load_3d(stage + c * kChunkBytes, &tmap_k, c * 64, kv_head, tok, bar(K_FULL0 + st));
         alive = tc::mbar_wait(bar(V_EMPTY0 + st), ph, status, 42);
         if (!alive) break;
+        DFT_TRACE_AT(j, 1);
         tc::mbar_arrive_expect_tx(bar(V_FULL0 + st), kVBytes);
 #pragma unroll
         for (int c = 0; c < 2; ++c) tc::tma_load_3d(stage + L::kQBytes + c * kChunkBytes, &tmap_v, c * 64, kv_head, tok, bar(V_FULL0 + st));
@@ -172,11 +189,13 @@ dense_fwd_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid_co
         __syncwarp();
       }
       tc::tc_fence_after();
+      if (lane == 0) DFT_TRACE_AT(j, 4);
       if (tc::elect_one()) {
         if (st == 0) dense_pv_block<0, D_QK>(tmem, desc_v, idesc_o, j == 0);
         else dense_pv_block<1, D_QK>(tmem, desc_v, idesc_o, j == 0);
         tc::tc_commit(bar(V_EMPTY0 + st));
         tc::tc_commit(bar(PV_DONE));
+        DFT_TRACE_AT(j, 5);
       }
       __syncwarp();
     };
@@ -187,11 +206,13 @@ dense_fwd_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid_co
       // the S buffer of this stage was last read as P by the P V of block j-2, issued earlier by
       // this thread: the tensor pipe runs them in order
       tc::tc_fence_after();
+      if (lane == 0) DFT_TRACE_AT(j, 2);
       if (tc::elect_one()) {
         if (st == 0) dense_s_block<0, D_QK>(tmem, desc_q, desc_k, idesc_s);
         else dense_s_block<1, D_QK>(tmem, desc_q, desc_k, idesc_s);
         tc::tc_commit(bar(S_FULL0 + st));
         tc::tc_commit(bar(K_EMPTY0 + st));
+        DFT_TRACE_AT(j, 3);
       }
       __syncwarp();
       if (j > 0) issue_pv(j - 1);
@@ -199,40 +220,62 @@ dense_fwd_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid_co
     if (alive && nblk > 0) issue_pv(nblk - 1);
   } else {
     // ================================ softmax / epilogue ================================
-    const int row = m_base + tid;                              // query row within its sequence
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    // Eight warps: warp w reads the TMEM lane quarter w % 4 (rows 32 (w % 4) ..), warps 0-3 the key
+    // columns [0,64) of a block and warps 6-9 the columns [64,128).  The two threads of a row exchange
+    // their maxima (and at the end their sums) through shared memory.
+    const int ch = warp >= 6 ? 1 : 0;                          // column half
+    const int rl = (warp & 3) * 32 + lane;                     // row within the tile = TMEM lane
+    const int row = m_base + rl;                               // query row within its sequence
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     // number of keys this row may see: bottom-right aligned causal mask, clipped to the sequence
     const int limit = p.is_causal ? max(0, min(lk, row + (lk - lq) + 1)) : lk;
     float m_run = neg_inf();     // running maximum (base-2 scaled logits)
     float m_used = 0.f;          // the maximum O and l are currently scaled with
-    float l_run = 0.f;
-    bool alive = true;
-    for (int j = 0; j < nblk && alive; ++j) {
+    float l_run = 0.f;           // this thread's share of the row sum
+    bool aborted = false;        // uniform over the softmax threads: only read right after a bar_sync
+    for (int j = 0; j < nblk && !aborted; ++j) {
       const int st = j & 1;
       const uint32_t s_addr = tmem + lane_addr + TMEM_S + st * 128;
-      alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(S_FULL0 + st), (j >> 1) & 1, status, 47));
-      if (!alive) break;
-      tc::tc_fence_after();
-      uint32_t sv[4][32];
+      uint32_t sv[2][32];
+      if (tc::mbar_wait(bar(S_FULL0 + st), (j >> 1) & 1, status, 47)) {
+        if (tid == 0) DFT_TRACE_AT(j, 6);
+        tc::tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tc::tmem_ld32(s_addr + c * 32, sv[c]);
-      tc::tmem_wait_ld();
-      const int cnt = limit - j * 128;                         // visible keys of this block: [0, cnt)
-      const bool full = __all_sync(0xffffffffu, cnt >= 128);
-      float mx = neg_inf();
+        for (int c = 0; c < 2; ++c) tc::tmem_ld32(s_addr + ch * 64 + c * 32, sv[c]);
+        tc::tmem_wait_ld();
+      } else {
+        *sAbort = 1;
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sv[c][i] = 0u;
+      }
+      if (tid == 0) DFT_TRACE_AT(j, 7);
+      const int cnt = limit - j * 128 - ch * 64;               // visible keys among this thread's 64: [0, cnt)
+      const bool full = __all_sync(0xffffffffu, cnt >= 64);
+      float mx4[4] = {neg_inf(), neg_inf(), neg_inf(), neg_inf()};   // independent chains
       if (full) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
       } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < cnt) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+            if (c * 32 + i < cnt) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
       }
-      const float m_new = fmaxf(m_run, mx * p.scale_log2);
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+      float* xch = sXch + (j & 1) * 256;
+      xch[ch * 128 + rl] = mx;
+      // after this barrier both threads of a row also hold all their S values in registers, so P may
+      // overwrite the columns S came from
+      bar_sync(1, 256);
+      if (*sAbort) { aborted = true; break; }
+      if (tid == 0) DFT_TRACE_AT(j, 8);
+      mx = fmaxf(mx, xch[(ch ^ 1) * 128 + rl]);
+      const float m_new = fmaxf(m_run, mx);
       // O and l carry the scale 2^-m_used; it is moved only when the maximum grew by more than the
       // threshold (or when the first real value arrives after fully masked blocks)
       bool need = false;
@@ -244,15 +287,15 @@ dense_fwd_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid_co
       m_run = m_new;
       if (__any_sync(0xffffffffu, need)) {
         // the previous P V must be complete before O is rescaled
-        alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(PV_DONE), (j - 1) & 1, status, 48));
-        if (!alive) break;
+        if (!tc::mbar_wait(bar(PV_DONE), (j - 1) & 1, status, 48)) *sAbort = 1;
         const float m_next = need ? m_new : m_used;
         const float alpha = exp2f(m_used - m_next);
         m_used = m_next;
         l_run *= alpha;
         tc::tc_fence_after();
+        // each of the two warps of a lane quarter rescales its half of the O columns
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = ch * 2; c < ch * 2 + 2; ++c) {
           uint32_t ov[32];
           tc::tmem_ld32(tmem + lane_addr + TMEM_O + c * 32, ov);
           tc::tmem_wait_ld();
@@ -261,10 +304,11 @@ dense_fwd_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid_co
           tc::tmem_st32(tmem + lane_addr + TMEM_O + c * 32, ov);
         }
       }
-      // P = 2^(s * scale - m_used), written as bf16 pairs over the first 64 columns of the S buffer
-      float rs = 0.f;
+      if (tid == 0) DFT_TRACE_AT(j, 9);
+      // P = 2^(s * scale - m_used), written as bf16 pairs: key 64 ch + e of the block -> column 32 ch + e / 2
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -274,28 +318,38 @@ dense_fwd_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid_co
             if (c * 32 + 2 * i >= cnt) p0 = 0.f;
             if (c * 32 + 2 * i + 1 >= cnt) p1 = 0.f;
           }
-          rs += p0 + p1;
+          rs4[i & 3] += p0 + p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
-        tc::tmem_st16(s_addr + c * 16, pk);
+        tc::tmem_st16(s_addr + ch * 32 + c * 16, pk);
       }
-      l_run += rs;
+      l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+      if (tid == 0) DFT_TRACE_AT(j, 10);
       tc::tmem_wait_st();
       tc::tc_fence_before();
       tc::mbar_arrive(bar(P_FULL0 + st));
+      if (tid == 0) DFT_TRACE_AT(j, 11);
     }
 
     // ---- epilogue ---------------------------------------------------------------------------
-    bool have_o = nblk > 0 && alive;
+    // row sum over the two threads of a row (the barriers on both sides keep this use of the
+    // exchange buffer apart from the block loop)
+    bar_sync(1, 256);
+    sXch[ch * 128 + rl] = l_run;
+    bar_sync(1, 256);
+    if (*sAbort) aborted = true;
+    const float l = l_run + sXch[(ch ^ 1) * 128 + rl];
+    bool have_o = nblk > 0 && !aborted;
     if (have_o) {
-      have_o = __all_sync(0xffffffffu, tc::mbar_wait(bar(PV_DONE), (nblk - 1) & 1, status, 49));
+      have_o = tc::mbar_wait(bar(PV_DONE), (nblk - 1) & 1, status, 49);
       tc::tc_fence_after();
     }
+    have_o = __all_sync(0xffffffffu, have_o);
     const bool row_ok = row < lq;
-    const float inv = (l_run == 0.f || !have_o) ? 0.f : 1.f / l_run;
+    const float inv = (l == 0.f || !have_o) ? 0.f : 1.f / l;
     __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + (int64_t)(q0 + row) * p.o_stride_t + head * p.o_stride_h;
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int c = ch * 2; c < ch * 2 + 2; ++c) {
       uint32_t ov[32];
       if (have_o) {
         tc::tmem_ld32(tmem + lane_addr + TMEM_O + c * 32, ov);
@@ -316,8 +370,8 @@ dense_fwd_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid_co
         }
       }
     }
-    if (row_ok)
-      p.lse[(int64_t)(q0 + row) * p.lse_stride_t + head * p.lse_stride_h] = inv == 0.f ? neg_inf() : (log2f(l_run) + m_used) * kLn2;
+    if (row_ok && ch == 0)
+      p.lse[(int64_t)(q0 + row) * p.lse_stride_t + head * p.lse_stride_h] = inv == 0.f ? neg_inf() : (log2f(l) + m_used) * kLn2;
   }
 
   tc::tc_fence_before();
@@ -334,7 +388,7 @@ static cudaError_t launch_fwd_tc(const DenseKernelParams& p, const CUtensorMap& 
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
   if (e != cudaSuccess) return e;
   dim3 grid((p.max_seqlen_q + 127) / 128, p.h_q, p.batch);
-  kern<<<grid, 192, L::SMEM_BYTES, stream>>>(p, tq, tk, tv);
+  kern<<<grid, 320, L::SMEM_BYTES, stream>>>(p, tq, tk, tv);
   return cudaGetLastError();
 }
 
@@ -346,6 +400,12 @@ cudaError_t launch_dense_fwd_tc(const DenseKernelParams& p, cudaStream_t stream)
   if (p.d_qk == 192) return launch_fwd_tc<192>(p, tq, tk, tv, stream);
   return launch_fwd_tc<128>(p, tq, tk, tv, stream);
 }
+
+#ifdef FMLA_TRACE
+extern "C" int fmla_debug_read_dense_trace(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_dense_trace, sizeof(long long) * n);
+}
+#endif
 
 cudaError_t read_dense_tc_status(int* host_status, bool reset) {
   cudaError_t e = cudaMemcpyFromSymbol(host_status, g_dense_tc_status, sizeof(int));
