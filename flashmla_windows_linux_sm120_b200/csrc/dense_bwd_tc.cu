@@ -59,6 +59,17 @@ struct Layout {
 
 __device__ int g_dense_bwd_tc_status = 0;
 
+// Optional timeline of the first steps of CTA (0,0,0) of the dQ kernel, compiled in with -DFMLA_TRACE only.
+#ifdef FMLA_TRACE
+__device__ long long g_dense_bwd_trace[64 * 16];
+#define DBT_TRACE_AT(blk, slot)                                                          \
+  do {                                                                                     \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (blk) < 64) g_dense_bwd_trace[(blk) * 16 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define DBT_TRACE_AT(blk, slot) do {} while (0)
+#endif
+
 // ---- 1. delta[h, t] = sum_d dO * O --------------------------------------------------------------
 __global__ void __launch_bounds__(256) dense_bwd_delta_tc_kernel(const __grid_constant__ DenseKernelParams p) {
   const int warp = (blockIdx.x * 256 + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -108,15 +119,17 @@ __device__ __forceinline__ void mma_tmem_stg(uint32_t d_tmem, uint32_t a_tmem, u
 }
 
 // ---- 2. dQ ------------------------------------------------------------------------------------------
-// grid (ceil(max_seqlen_q/128), h_q, batch), 192 threads.  Resident: Q, dO tiles of 128 queries.
-// Per step (64 keys): S = Q K^T and dP = dO V^T into one of two TMEM buffer pairs, dS over S, then
-// dQ += dS K.  TMEM: dQ = [0, D_QK), buffer b: S = [192 + 128 b, +64), dP = [256 + 128 b, +64).
+// grid (ceil(max_seqlen_q/128), h_q, batch), 224 threads (warps 0-3 element-wise, 4 TMA, 5 and 6 MMA).
+// Resident: Q, dO tiles of 128 queries.
+// Per step (64 keys): S = Q K^T and dP = dO V^T into one of two TMEM buffer pairs, dS (bf16) into one of two
+// slots, then dQ += dS K.  TMEM: dQ = [0, D_QK), buffer b: S = [192 + 128 b, +64), dP = [256 + 128 b, +64),
+// dS slot b = [448 + 32 b, +32).
 namespace dbt {
-enum BarQ { Q_RES_FULL = 0, Q_KV_FULL0, Q_KV_EMPTY0 = Q_KV_FULL0 + kStages, Q_SD_FULL0 = Q_KV_EMPTY0 + kStages, Q_SD_FULL1, Q_DS_FULL0, Q_DS_FULL1, Q_DONE, Q_NUM_BARS };
+enum BarQ { Q_RES_FULL = 0, Q_KV_FULL0, Q_KV_EMPTY0 = Q_KV_FULL0 + kStages, Q_SD_FULL0 = Q_KV_EMPTY0 + kStages, Q_SD_FULL1, Q_DS_FULL0, Q_DS_FULL1, Q_BUF_FREE0, Q_BUF_FREE1, Q_DONE, Q_NUM_BARS };
 }
 
 template <int D_QK>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(224, 1)
 dense_bwd_dq_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid_constant__ CUtensorMap tmap_q,
                        const __grid_constant__ CUtensorMap tmap_do, const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v) {
@@ -154,7 +167,7 @@ dense_bwd_dq_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem = *sTmem;
-  constexpr int TM_DQ = 0, TM_SD = 192;
+  constexpr int TM_DQ = 0, TM_SD = 192, TM_DS = 448;
 
   if (warp == 4) {
     // ================================ TMA producer =====================================
@@ -171,6 +184,7 @@ dense_bwd_dq_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid
         const int tok = k0 + j * 64;
         alive = tc::mbar_wait(bar(Q_KV_EMPTY0 + st), ((j / kStages) & 1) ^ 1, status, 51);
         if (!alive) break;
+        DBT_TRACE_AT(j, 0);
         tc::mbar_arrive_expect_tx(bar(Q_KV_FULL0 + st), L::kStage);
 #pragma unroll
         for (int c = 0; c < L::NCH; ++c) tc::tma_load_3d(stage + c * kStgChunk, &tmap_k, c * 64, head, tok, bar(Q_KV_FULL0 + st));
@@ -178,8 +192,8 @@ dense_bwd_dq_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid
         for (int c = 0; c < 2; ++c) tc::tma_load_3d(stage + L::kStgA + c * kStgChunk, &tmap_v, c * 64, head, tok, bar(Q_KV_FULL0 + st));
       }
     }
-  } else if (warp == 5) {
-    // ================================ MMA issuer =======================================
+  } else if (warp == 5 || warp == 6) {
+    // ================================ MMA issuers =======================================
     constexpr uint32_t idesc_sd = tc::idesc_bf16_f32(128, 64, 0, 0);
     constexpr uint32_t idesc_dq = tc::idesc_bf16_f32(128, D_QK, 0, 1);
     const uint64_t desc_q = tc::smem_desc_sw128(sQ, 16, 1024);
@@ -189,43 +203,53 @@ dense_bwd_dq_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid
     const uint64_t desc_kt = tc::smem_desc_sw128(sStg, kStgChunk, 1024);              // K tile of stage 0, MN-major (B of dQ)
     bool alive = nblk > 0;
     if (alive) alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_RES_FULL), 0, status, 52));
-    auto issue_dq = [&](int j) {
-      const int st = j % kStages, bf = j & 1;
-      alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_DS_FULL0 + bf), (j >> 1) & 1, status, 53));
-      if (!alive) return;
-      tc::tc_fence_after();
-      if (tc::elect_one()) {
-        dispatch_stage_buffer(st, bf, [&](auto ST, auto BF) {
-          mma_tmem_stg(tmem + TM_DQ, tmem + TM_SD + decltype(BF)::value * 128, tc::desc_advance(desc_kt, decltype(ST)::value * L::kStage),
-                       idesc_dq, j == 0);
-        });
-        tc::tc_commit(bar(Q_KV_EMPTY0 + st));
+    // Two issuing warps: warp 5 the first GEMMs of a step (S, dP), warp 6 the second one (dQ).  Each
+    // wait on an mbarrier costs the issuing warp a few hundred cycles in which the tensor pipe would
+    // otherwise idle; with two warps the waits of one overlap the instructions of the other.
+    if (warp == 5) {
+      for (int j = 0; j < nblk && alive; ++j) {
+        const int st = j % kStages, bf = j & 1;
+        // the tile has landed, and the S / dP buffer pair bf is free (the element-wise warps have read step
+        // j-2 out of it)
+        alive = tc::mbar_wait2(bar(Q_KV_FULL0 + st), (j / kStages) & 1, bar(Q_DS_FULL0 + bf), ((j >> 1) & 1) ^ 1, status, 54);
+        if (!alive) break;
+        // K rows past the end of the sequence must be exact zeros for dQ += dS K
+        if (lk - j * 64 < 64) zero_stage_tail(smem + L::STG_OFF + st * L::kStage, L::NCH, lk - j * 64, lane);
+        tc::tc_fence_after();
+        if (lane == 0) DBT_TRACE_AT(j, 2);
+        if (tc::elect_one()) {
+          dispatch_stage_buffer(st, bf, [&](auto ST, auto BF) {
+            constexpr int kOff = decltype(ST)::value * L::kStage, kCol = TM_SD + decltype(BF)::value * 128;
+            mma_res_stg<L::NCH>(tmem + kCol, desc_q, tc::desc_advance(desc_k, kOff), idesc_sd);
+            mma_res_stg<2>(tmem + kCol + 64, desc_do, tc::desc_advance(desc_v, kOff), idesc_sd);
+          });
+          tc::tc_commit(bar(Q_SD_FULL0 + bf));
+          DBT_TRACE_AT(j, 3);
+        }
+        __syncwarp();
       }
-      __syncwarp();
-    };
-    for (int j = 0; j < nblk && alive; ++j) {
-      const int st = j % kStages, bf = j & 1;
-      alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_KV_FULL0 + st), (j / kStages) & 1, status, 54));
-      if (!alive) break;
-      // K rows past the end of the sequence must be exact zeros for dQ += dS K
-      if (lk - j * 64 < 64) zero_stage_tail(smem + L::STG_OFF + st * L::kStage, L::NCH, lk - j * 64, lane);
-      tc::tc_fence_after();
-      if (tc::elect_one()) {
-        // the S / dP buffer pair bf was last read (as dS) by the dQ instructions of step j-2, issued earlier
-        // by this thread: the tensor pipe runs them in order
-        dispatch_stage_buffer(st, bf, [&](auto ST, auto BF) {
-          constexpr int kOff = decltype(ST)::value * L::kStage, kCol = TM_SD + decltype(BF)::value * 128;
-          mma_res_stg<L::NCH>(tmem + kCol, desc_q, tc::desc_advance(desc_k, kOff), idesc_sd);
-          mma_res_stg<2>(tmem + kCol + 64, desc_do, tc::desc_advance(desc_v, kOff), idesc_sd);
-        });
-        tc::tc_commit(bar(Q_SD_FULL0 + bf));
+    } else {
+      for (int j = 0; j < nblk && alive; ++j) {
+        const int st = j % kStages, bf = j & 1;
+        if (lane == 0) DBT_TRACE_AT(j, 10);
+        alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_DS_FULL0 + bf), (j >> 1) & 1, status, 53));
+        if (!alive) break;
+        if (lane == 0) DBT_TRACE_AT(j, 11);
+        tc::tc_fence_after();
+        if (lane == 0) DBT_TRACE_AT(j, 4);
+        if (tc::elect_one()) {
+          dispatch_stage_buffer(st, bf, [&](auto ST, auto BF) {
+            mma_tmem_stg(tmem + TM_DQ, tmem + TM_DS + decltype(BF)::value * 32, tc::desc_advance(desc_kt, decltype(ST)::value * L::kStage),
+                         idesc_dq, j == 0);
+          });
+          tc::tc_commit(bar(Q_KV_EMPTY0 + st));
+          tc::tc_commit(bar(Q_BUF_FREE0 + bf));
+          if (j == nblk - 1) tc::tc_commit(bar(Q_DONE));
+          DBT_TRACE_AT(j, 5);
+        }
+        __syncwarp();
       }
-      __syncwarp();
-      if (j > 0) issue_dq(j - 1);
     }
-    if (alive && nblk > 0) issue_dq(nblk - 1);
-    if (alive && tc::elect_one()) tc::tc_commit(bar(Q_DONE));
-    __syncwarp();
   } else {
     // ================================ element-wise / epilogue ==========================
     const int row = m_base + tid;
@@ -238,8 +262,12 @@ dense_bwd_dq_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid
     for (int j = 0; j < nblk && alive; ++j) {
       const int st = j & 1;
       const uint32_t sd_addr = tmem + lane_addr + TM_SD + st * 128;
-      alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_SD_FULL0 + st), (j >> 1) & 1, status, 55));
+      // S and dP of this step are there, and the dS slot st is free (it was last read by the dQ
+      // instructions of step j-2; dS has slots of its own so that the fp32 buffers are free again as
+      // soon as they have been read)
+      alive = tc::mbar_wait2(bar(Q_SD_FULL0 + st), (j >> 1) & 1, bar(Q_BUF_FREE0 + st), ((j >> 1) & 1) ^ 1, status, 55);
       if (!alive) break;
+      if (tid == 0) DBT_TRACE_AT(j, 6);
       tc::tc_fence_after();
       uint32_t sv[2][32], dp[2][32];
 #pragma unroll
@@ -248,6 +276,7 @@ dense_bwd_dq_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid
         tc::tmem_ld32(sd_addr + 64 + c * 32, dp[c]);
       }
       tc::tmem_wait_ld();
+      if (tid == 0) DBT_TRACE_AT(j, 7);
       const int cnt = limit - j * 64;                          // visible keys of this block: [0, cnt)
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -261,11 +290,13 @@ dense_bwd_dq_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid
           const float d1 = (c * 32 + 2 * i + 1 < cnt) ? p1 * (__uint_as_float(dp[c][2 * i + 1]) - dl) : 0.f;
           pk[i] = pack_bf16x2(d0, d1);
         }
-        tc::tmem_st16(sd_addr + c * 16, pk);
+        tc::tmem_st16(tmem + lane_addr + TM_DS + st * 32 + c * 16, pk);
       }
+      if (tid == 0) DBT_TRACE_AT(j, 8);
       tc::tmem_wait_st();
       tc::tc_fence_before();
       tc::mbar_arrive(bar(Q_DS_FULL0 + st));
+      if (tid == 0) DBT_TRACE_AT(j, 9);
     }
     bool have = nblk > 0 && alive;
     if (have) {
@@ -562,7 +593,7 @@ static cudaError_t launch_bwd_tc(const DenseKernelParams& p, cudaStream_t stream
   const int rows = p.total_q * p.h_q;
   dense_bwd_delta_tc_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(p);
   kk<<<dim3((p.max_seqlen_k + 127) / 128, p.h_q, p.batch), 192, L::SMEM_BYTES, stream>>>(p, k128, v128, q64, do64);
-  kq<<<dim3((p.max_seqlen_q + 127) / 128, p.h_q, p.batch), 192, L::SMEM_BYTES, stream>>>(p, q128, do128, k64, v64);
+  kq<<<dim3((p.max_seqlen_q + 127) / 128, p.h_q, p.batch), 224, L::SMEM_BYTES, stream>>>(p, q128, do128, k64, v64);
   return cudaGetLastError();
 }
 
@@ -570,6 +601,12 @@ cudaError_t launch_dense_bwd_tc(const DenseKernelParams& p, cudaStream_t stream)
   if (p.d_qk == 192) return launch_bwd_tc<192>(p, stream);
   return launch_bwd_tc<128>(p, stream);
 }
+
+#ifdef FMLA_TRACE
+extern "C" int fmla_debug_read_dense_bwd_trace(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_dense_bwd_trace, sizeof(long long) * n);
+}
+#endif
 
 cudaError_t read_dense_bwd_tc_status(int* host_status, bool reset) {
   cudaError_t e = cudaMemcpyFromSymbol(host_status, g_dense_bwd_tc_status, sizeof(int));

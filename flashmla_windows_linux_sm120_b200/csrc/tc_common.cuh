@@ -57,6 +57,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
   return false;
 }
 
+// Waits (bounded) for two barrier phases at once: lanes 0 and 1 each poll one barrier without blocking and
+// a ballot shares the outcome, so that the two waits cost one round trip instead of two.  Whole warp, converged.
+__device__ __forceinline__ bool mbar_wait2(uint32_t bar_a, uint32_t par_a, uint32_t bar_b, uint32_t par_b, int* status, int code) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t b = lane == 0 ? bar_a : bar_b, pp = lane == 0 ? par_a : par_b;
+  for (int i = 0; i < kSpinLimit; ++i) {
+    const bool hit = lane < 2 && mbar_test_wait(b, pp);
+    if ((__ballot_sync(0xffffffffu, hit) & 3u) == 3u) return true;
+  }
+  if (status && lane == 0) atomicCAS(status, 0, code);
+  return false;
+}
+
 // ---- TMA ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];\n" ::"l"(tmap) : "memory");
