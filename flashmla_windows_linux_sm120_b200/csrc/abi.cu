@@ -150,7 +150,8 @@ static int decode_impl(const fmla_decode_params* P, const fmla_peer_push* push, 
   FMLA_REQUIRE(a.d_v == 512, "Only head_size_v == 512 is supported");
   FMLA_REQUIRE(a.page_block_size == 64, "Currently page_block_size must be 64");
   FMLA_REQUIRE(a.h_q % a.h_k == 0, "Number of heads in key/value must divide number of heads in query");
-  if (a.q_dtype != FMLA_DTYPE_BF16) return fail(FMLA_ERR_UNSUPPORTED, "only bfloat16 queries are supported");
+  if (a.q_dtype != FMLA_DTYPE_BF16 && a.q_dtype != FMLA_DTYPE_FP16) return fail(FMLA_ERR_INVALID_ARGUMENT, "q_dtype must be FMLA_DTYPE_BF16 or FMLA_DTYPE_FP16");
+  if (a.q_dtype == FMLA_DTYPE_FP16 && (sparse || a.is_fp8)) return fail(FMLA_ERR_UNSUPPORTED, "float16 queries are supported for the dense (float16 cache) decode only");
   if (sparse != (a.is_fp8 != 0)) return fail(FMLA_ERR_UNSUPPORTED, "supported combinations: dense BF16 cache, or sparse (indices) FP8 cache");
   FMLA_REQUIRE(a.q && a.kcache && a.seqlens_k && a.tile_scheduler_metadata && a.num_splits && a.lse_accum && a.o_accum, "null pointer");
   FMLA_REQUIRE(push || (a.out && a.softmax_lse), "null output pointer");
@@ -179,6 +180,7 @@ static int decode_impl(const fmla_decode_params* P, const fmla_peer_push* push, 
   k.is_causal = (a.is_causal && a.s_q > 1) ? 1 : 0;   // s_q == 1 => causal is a no-op (pybind.cpp:501)
   k.topk = sparse ? a.topk : -1;
   k.scale_log2 = a.softmax_scale * 1.4426950408889634f;
+  k.is_f16 = a.q_dtype == FMLA_DTYPE_FP16 ? 1 : 0;
   k.q = a.q; k.q_stride_b = a.q_stride_b; k.q_stride_s = a.q_stride_s; k.q_stride_h = a.q_stride_h;
   k.kcache = a.kcache; k.k_stride_block = a.k_stride_block; k.k_stride_row = a.k_stride_row; k.k_stride_head = a.k_stride_head;
   k.block_table = a.block_table; k.block_table_stride_b = a.block_table_stride_b;

@@ -18,7 +18,7 @@ constexpr int kCombineWarps = 8;
 // lse_part(i) / o_part(i) address part i of this row.
 template <class LseAt, class OAt>
 __device__ __forceinline__ void combine_row(int nparts, LseAt lse_at, OAt o_at, float* s_w, __nv_bfloat16* out_row,
-                                            float* lse_out) {
+                                            float* lse_out, bool f16 = false) {
   const int lane = threadIdx.x & 31;
   float mx = neg_inf();
   for (int i = lane; i < nparts; i += 32) mx = fmaxf(mx, lse_at(i));
@@ -52,7 +52,9 @@ __device__ __forceinline__ void combine_row(int nparts, LseAt lse_at, OAt o_at, 
   }
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    uint2 packed = make_uint2(pack_bf16x2(acc[j].x, acc[j].y), pack_bf16x2(acc[j].z, acc[j].w));
+    // out_row addresses 16-bit elements: bf16, or fp16 when the queries were fp16
+    uint2 packed = f16 ? make_uint2(pack_f16x2(acc[j].x, acc[j].y), pack_f16x2(acc[j].z, acc[j].w))
+                       : make_uint2(pack_bf16x2(acc[j].x, acc[j].y), pack_bf16x2(acc[j].z, acc[j].w));
     *reinterpret_cast<uint2*>(out_row + (j * 32 + lane) * 4) = packed;
   }
 }
@@ -79,7 +81,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32) decode_combine_kernel(cons
       nparts, [&](int i) { return __ldg(lse_base + i * part_stride); },
       [&](int i) { return o_base + i * part_stride * 512; }, s_weights + warp * p.num_sm_parts,
       reinterpret_cast<__nv_bfloat16*>(p.out) + batch * p.o_stride_b + sq * p.o_stride_s + head * p.o_stride_h,
-      p.softmax_lse + ((int64_t)batch * p.h_q + head) * p.s_q + sq);
+      p.softmax_lse + ((int64_t)batch * p.h_q + head) * p.s_q + sq, p.is_f16 != 0);
 }
 
 __global__ void __launch_bounds__(kCombineWarps * 32)

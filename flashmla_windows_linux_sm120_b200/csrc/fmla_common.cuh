@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -62,6 +63,16 @@ __device__ __forceinline__ uint32_t swz_off(int row, int chunk, int row_bytes) {
   return static_cast<uint32_t>(row * row_bytes + (((chunk & ~7) | ((chunk ^ row) & 7)) << 4));
 }
 
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+// two floats -> one 32-bit word of the 16-bit output type (bf16, or fp16 when F16)
+template <bool F16>
+__device__ __forceinline__ uint32_t pack_16x2(float lo, float hi) {
+  if constexpr (F16) return pack_f16x2(lo, hi);
+  else return pack_bf16x2(lo, hi);
+}
 __device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
 __device__ __forceinline__ float pos_inf() { return __int_as_float(0x7f800000); }
 

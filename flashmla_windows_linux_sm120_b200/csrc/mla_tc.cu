@@ -190,7 +190,7 @@ __device__ __forceinline__ void s_block(uint32_t tmem, uint64_t desc_q, uint64_t
 
 // grid: kDense (s_q*ceil(hq_per_hk/64), h_k, parts), 192 threads;
 //       kSparseDecode (ceil(h_q/64), s_q, parts), 448 threads; kSparsePrefill (h_q/64, s_q), 448 threads
-template <int MODE>
+template <int MODE, bool F16>
 __global__ void __launch_bounds__(MODE == kDense ? 192 : 448, 1)
 mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtensorMap tmap_q,
               const __grid_constant__ CUtensorMap tmap_kv) {
@@ -414,8 +414,8 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
     }
   } else if (warp == 5) {
     // ================================ MMA issuer =======================================
-    constexpr uint32_t idesc_s = tc::idesc_bf16_f32(64, 64, 0, 0);
-    constexpr uint32_t idesc_o = tc::idesc_bf16_f32(64, 256, 0, 1);
+    constexpr uint32_t idesc_s = tc::idesc_bf16_f32(64, 64, 0, 0, F16);
+    constexpr uint32_t idesc_o = tc::idesc_bf16_f32(64, 256, 0, 1, F16);
     // descriptors of the operand bases; per-MMA addresses are constant offsets added to the low word
     const uint64_t desc_q = tc::smem_desc_sw128(sQ, 16, 1024);             // A of S: K-major
     const uint64_t desc_k = tc::smem_desc_sw128(sKV, 16, 1024);            // B of S: K-major (stage 0)
@@ -620,7 +620,7 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
         for (int i = 0; i < 16; ++i) {
           const float p0 = exp2f(s[2 * i] - m_used), p1 = exp2f(s[2 * i + 1] - m_used);
           rs += p0 + p1;
-          pk[i] = pack_bf16x2(p0, p1);
+          pk[i] = pack_16x2<F16>(p0, p1);
         }
         l_part += rs;
         if (!pv_done && !tc::mbar_wait(bar(P_EMPTY), (g & 1) ^ 1, status, 9)) *sAbort = 1;
@@ -680,10 +680,10 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
               uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(ov[q4 * 8 + 0]) * inv, __uint_as_float(ov[q4 * 8 + 1]) * inv);
-              v.y = pack_bf16x2(__uint_as_float(ov[q4 * 8 + 2]) * inv, __uint_as_float(ov[q4 * 8 + 3]) * inv);
-              v.z = pack_bf16x2(__uint_as_float(ov[q4 * 8 + 4]) * inv, __uint_as_float(ov[q4 * 8 + 5]) * inv);
-              v.w = pack_bf16x2(__uint_as_float(ov[q4 * 8 + 6]) * inv, __uint_as_float(ov[q4 * 8 + 7]) * inv);
+              v.x = pack_16x2<F16>(__uint_as_float(ov[q4 * 8 + 0]) * inv, __uint_as_float(ov[q4 * 8 + 1]) * inv);
+              v.y = pack_16x2<F16>(__uint_as_float(ov[q4 * 8 + 2]) * inv, __uint_as_float(ov[q4 * 8 + 3]) * inv);
+              v.z = pack_16x2<F16>(__uint_as_float(ov[q4 * 8 + 4]) * inv, __uint_as_float(ov[q4 * 8 + 5]) * inv);
+              v.w = pack_16x2<F16>(__uint_as_float(ov[q4 * 8 + 6]) * inv, __uint_as_float(ov[q4 * 8 + 7]) * inv);
               *reinterpret_cast<uint4*>(o_final + col + q4 * 8) = v;
             }
           } else {
@@ -748,9 +748,9 @@ static bool make_map_4d(CUtensorMap* m, const void* base, uint64_t d1, uint64_t 
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int MODE>
+template <int MODE, bool F16 = false>
 static cudaError_t launch_tc(const TcParams& P, const CUtensorMap& tq, const CUtensorMap& tkv, dim3 grid, cudaStream_t stream) {
-  auto kern = mla_tc_kernel<MODE>;
+  auto kern = mla_tc_kernel<MODE, F16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dtc::SMEM_BYTES);
   if (e != cudaSuccess) return e;
   kern<<<grid, MODE == kDense ? 192 : 448, dtc::SMEM_BYTES, stream>>>(P, tq, tkv);
@@ -767,6 +767,8 @@ cudaError_t launch_decode_dense_tc(const DecodeKernelParams& p, cudaStream_t str
   if (!make_map_4d(&tkv, p.kcache, p.h_k, 64, p.num_blocks, p.k_stride_head, p.k_stride_row, p.k_stride_block, 1, 64))
     return cudaErrorInvalidValue;
   const int n_hb = (p.hq_per_hk + 63) / 64;
+  // the tensor maps only move 16-bit elements: one map type serves bf16 and fp16
+  if (p.is_f16) return launch_tc<kDense, true>(P, tq, tkv, dim3(p.s_q * n_hb, p.h_k, p.num_sm_parts), stream);
   return launch_tc<kDense>(P, tq, tkv, dim3(p.s_q * n_hb, p.h_k, p.num_sm_parts), stream);
 }
 

@@ -102,8 +102,9 @@ def fwd_kvcache_mla(q: torch.Tensor, kcache: torch.Tensor, head_size_v: int, seq
     if sparse:
         _require(indices.dim() == 3 and indices.shape[0] == b and indices.shape[1] == s_q, "indices must be [b, s_q, topk]")
         topk = indices.shape[2]
-    if q.dtype != torch.bfloat16:
-        raise RuntimeError("flashmla_b200: unsupported configuration: only bfloat16 queries are supported")
+    if q.dtype == torch.float16 and (sparse or is_fp8):
+        raise RuntimeError("flashmla_b200: unsupported configuration: float16 queries are supported for the dense "
+                           "(float16 cache) decode only")
 
     num_sm_parts = tile_scheduler_metadata.shape[0]
     with torch.cuda.device(q.device):
@@ -115,7 +116,8 @@ def fwd_kvcache_mla(q: torch.Tensor, kcache: torch.Tensor, head_size_v: int, seq
         p = DecodeParams()
         p.b, p.s_q, p.h_q, p.h_k, p.d, p.d_v = b, s_q, h_q, h_k, d, int(head_size_v)
         p.num_blocks, p.page_block_size = num_blocks, page
-        p.is_causal, p.is_fp8, p.topk, p.q_dtype = int(bool(is_causal)), int(bool(is_fp8)), topk, 0
+        p.is_causal, p.is_fp8, p.topk = int(bool(is_causal)), int(bool(is_fp8)), topk
+        p.q_dtype = 1 if q.dtype == torch.float16 else 0
         p.softmax_scale = float(softmax_scale)
         p.q, p.q_stride_b, p.q_stride_s, p.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1), q.stride(2)
         p.kcache = kcache.data_ptr()

@@ -90,7 +90,7 @@ typedef struct fmla_decode_params {
   int32_t is_causal;               /* ignored when s_q == 1 (pybind.cpp:501)         */
   int32_t is_fp8;                  /* cache holds 656-byte FP8 token records         */
   int32_t topk;                    /* -1 = dense; else indices[...,topk] are used    */
-  int32_t q_dtype;                 /* FMLA_DTYPE_BF16                                */
+  int32_t q_dtype;                 /* FMLA_DTYPE_BF16, or FMLA_DTYPE_FP16 (dense only) */
   float softmax_scale;
 
   const void* q;                   /* [b, s_q, h_q, d]; last dim contiguous          */

@@ -78,7 +78,8 @@ def decode_ref(cache_seqlens: torch.Tensor, block_table: torch.Tensor, q: torch.
         o, l = _attend(q[i].transpose(0, 1), kv.transpose(0, 1), dv, mask, softmax_scale)
         out[i] = o.transpose(0, 1)
         lse[i] = l
-    return out.to(torch.bfloat16), lse
+    # the result takes the dtype of q (bf16, or fp16 for fp16 inputs), tests/test_flash_mla_decoding.py:347-359
+    return out.to(q.dtype if q.dtype in (torch.bfloat16, torch.float16) else torch.bfloat16), lse
 
 
 def decode_sparse_physical_ref(q: torch.Tensor, blocked_k: torch.Tensor, indices: torch.Tensor,

@@ -56,6 +56,23 @@ def test_dense_decode(b, s_q, s_k, varlen, causal, h_q, h_kv):
     scheduler.check_schedule_invariants(md.tolist(), ns.tolist(), d.cache_seqlens.tolist())
 
 
+@pytest.mark.parametrize("b,s_q,s_k,varlen,causal,h_q,h_kv", [
+    (6, 1, 1500, True, False, 128, 1),
+    (2, 2, 4096, True, True, 128, 1),
+    (2, 2, 260, True, True, 32, 2),
+])
+def test_dense_decode_fp16(b, s_q, s_k, varlen, causal, h_q, h_kv):
+    """float16 queries and cache (the reference test's --dtype fp16, tests/test_flash_mla_decoding.py:347-359)."""
+    t = gen.DecodeCase(b=b, s_q=s_q, s_k=s_k, is_varlen=varlen, is_causal=causal, h_q=h_q, h_kv=h_kv)
+    d = gen.make_decode_case(t)
+    d.q = d.q.to(torch.float16)
+    d.blocked_k = d.blocked_k.to(torch.float16)
+    out, lse, md, ns = _run_dense(d, t)
+    assert out.dtype == torch.float16
+    ref_out, ref_lse = decode.decode_ref(d.cache_seqlens, d.block_table, d.q, d.blocked_k, t.dv, causal)
+    U.assert_out_lse(out, lse, ref_out, ref_lse)
+
+
 def test_dense_decode_zero_length_requests():
     t = gen.DecodeCase(b=16, s_q=2, s_k=500, is_varlen=True, is_causal=True, zero_seqlen=True)
     d = gen.make_decode_case(t)
@@ -138,5 +155,5 @@ def test_argument_errors():
         fm.flash_mla_with_kvcache(d.q.cuda()[..., :512].contiguous(), d.blocked_k.cuda(), d.block_table.cuda(), lens, 512, md, ns)
     with pytest.raises(RuntimeError):
         fm.flash_mla_with_kvcache(d.q.cuda(), d.blocked_k.cuda(), d.block_table.cuda().long(), lens, 512, md, ns)
-    with pytest.raises(RuntimeError):
-        fm.flash_mla_with_kvcache(d.q.cuda().half(), d.blocked_k.cuda().half(), d.block_table.cuda(), lens, 512, md, ns)
+    with pytest.raises(RuntimeError):   # query and cache must have one dtype
+        fm.flash_mla_with_kvcache(d.q.cuda().half(), d.blocked_k.cuda(), d.block_table.cuda(), lens, 512, md, ns)
