@@ -81,6 +81,40 @@ def test_dense_neighbour_sequence_does_not_leak(causal):
     assert torch.equal(dq[:lq0], a_dq) and torch.equal(dk[:lk0], a_dk) and torch.equal(dvv[:lk0], a_dv)
 
 
+def test_dense_packed_inputs_are_read_in_place():
+    """flash_attn_varlen_qkvpacked_func / kvpacked_func hand strided views of one packed tensor to the kernels
+    (no copy): results and gradients equal those of the same values passed as separate tensors, bit for bit."""
+    import flashmla_windows_linux_sm120_b200 as fm
+    c = gen.make_dense_case(gen.DenseCase(b=2, mean_sq=180, mean_sk=180, varlen=False, h=4, h_k=4, d=192, dv=128, causal=True))
+    cu, mx = c["cu_q"].cuda(), c["max_q"]
+    q, k, v, d_out = (c[n].cuda() for n in ("q", "k", "v", "d_out"))
+    qs, ks, vs = (t.clone().requires_grad_() for t in (q, k, v))
+    out, lse = fm.flash_attn_varlen_func(qs, ks, vs, cu, cu, mx, mx, softmax_scale=c["scale"], causal=True)
+    out.backward(d_out)
+
+    qkv = torch.cat([q, k, v], dim=-1).requires_grad_()
+    out_p, lse_p = fm.flash_attn_varlen_qkvpacked_func(qkv, cu, mx, 192, softmax_scale=c["scale"], causal=True)
+    out_p.backward(d_out)
+    assert torch.equal(out_p, out) and torch.equal(lse_p, lse)
+    assert torch.equal(qkv.grad[..., :192], qs.grad) and torch.equal(qkv.grad[..., 192:384], ks.grad)
+    assert torch.equal(qkv.grad[..., 384:], vs.grad)
+
+    qk, kv = q.clone().requires_grad_(), torch.cat([k, v], dim=-1).requires_grad_()
+    out_k, lse_k = fm.flash_attn_varlen_kvpacked_func(qk, kv, cu, cu, mx, mx, 192, softmax_scale=c["scale"], causal=True)
+    out_k.backward(d_out)
+    assert torch.equal(out_k, out) and torch.equal(lse_k, lse)
+    assert torch.equal(qk.grad, qs.grad) and torch.equal(kv.grad[..., :192], ks.grad) and torch.equal(kv.grad[..., 192:], vs.grad)
+
+
+def test_dense_fwd_gqa_32_over_4():
+    """the reference grid's GQA shape (tests/test_fmha_sm100.py:189): 32 query heads over 4 kv heads"""
+    c = gen.make_dense_case(gen.DenseCase(b=2, mean_sq=200, mean_sk=330, varlen=True, h=32, h_k=4, d=192, dv=128, causal=True))
+    out, lse, _ = _run(c, True, False)
+    r_out, r_lse = dense.dense_fwd_ref(c["q"], c["k"], c["v"], c["cu_q"], c["cu_k"], True, c["scale"])
+    assert check_is_allclose("out", out, r_out, **TOL)
+    assert check_is_allclose("lse", lse, r_lse, **LSE_TOL)
+
+
 @pytest.mark.parametrize("d", [192, 128])
 def test_dense_fwd_gqa(d):
     c = gen.make_dense_case(gen.DenseCase(b=2, mean_sq=150, mean_sk=260, varlen=True, h=8, h_k=2, d=d, dv=128, causal=True))
