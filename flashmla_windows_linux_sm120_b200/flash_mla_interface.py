@@ -130,7 +130,7 @@ def flash_attn_varlen_func(q, k, v, cu_seqlens_qo, cu_seqlens_kv, max_seqlen_qo,
     """Dense varlen MHA, forward + autograd backward (reference: flash_mla_interface.py:503-523).
     Returns (out [total_q, h, d_v], lse [total_q, h] natural log)."""
     assert dropout_p == 0.0
-    assert not deterministic
+    del deterministic   # accepted: the backward here is always bitwise reproducible (the reference asserts False)
     return FlashAttnVarlenFunc.apply(q, k, v, cu_seqlens_qo, cu_seqlens_kv, max_seqlen_qo, max_seqlen_kv, causal,
                                      softmax_scale, is_varlen)
 
@@ -139,7 +139,7 @@ def flash_attn_varlen_qkvpacked_func(qkv, cu_seqlens, max_seqlen, head_dim_qk, d
                                      causal=False, deterministic=False, is_varlen=True):
     """reference: flash_mla_interface.py:526-545.  qkv [total, h, 2*head_dim_qk + d_v]."""
     assert dropout_p == 0.0
-    assert not deterministic
+    del deterministic   # accepted: the backward here is always bitwise reproducible (the reference asserts False)
     return FlashAttnVarlenFunc.apply(qkv[:, :, :head_dim_qk], qkv[:, :, head_dim_qk:head_dim_qk * 2],
                                      qkv[:, :, head_dim_qk * 2:], cu_seqlens, cu_seqlens, max_seqlen, max_seqlen,
                                      causal, softmax_scale, is_varlen)
@@ -150,6 +150,6 @@ def flash_attn_varlen_kvpacked_func(q, kv, cu_seqlens_qo, cu_seqlens_kv, max_seq
                                     is_varlen=True):
     """reference: flash_mla_interface.py:548-566.  kv [total_k, h_k, head_dim_qk + d_v]."""
     assert dropout_p == 0.0
-    assert not deterministic
+    del deterministic   # accepted: the backward here is always bitwise reproducible (the reference asserts False)
     return FlashAttnVarlenFunc.apply(q, kv[:, :, :head_dim_qk], kv[:, :, head_dim_qk:], cu_seqlens_qo, cu_seqlens_kv,
                                      max_seqlen_qo, max_seqlen_kv, causal, softmax_scale, is_varlen)

@@ -145,6 +145,35 @@ def test_sparse_fp8_decode_golden(name):
     U.assert_out_lse(out.cpu(), lse.cpu(), g["out"], g["lse"])
 
 
+def test_decode_step_replays_from_a_cuda_graph():
+    """Scheduler + attention + combine of one decode step captured into a CUDA graph (after one eager warm-up
+    call) and replayed on new query values give the eager result bit for bit."""
+    fm = _api()
+    t = gen.DecodeCase(b=8, s_q=1, s_k=900, is_varlen=True, h_q=128)
+    d = gen.make_decode_case(t)
+    lens, bt, cache = d.cache_seqlens.cuda(), d.block_table.cuda(), d.blocked_k.cuda()
+    q_static = d.q.cuda().clone()
+
+    def step(q):
+        md, ns = fm.get_mla_metadata(lens, t.s_q * t.h_q // t.h_kv, t.h_kv)
+        return fm.flash_mla_with_kvcache(q, cache, bt, lens, t.dv, md, ns, causal=False)
+
+    step(q_static)                       # warm-up: driver entry points, function attributes, allocator pools
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out_g, lse_g = step(q_static)
+    for seed in (1, 2):
+        torch.manual_seed(seed)
+        q_new = (torch.randn_like(q_static.float()) / 10).to(q_static.dtype)
+        q_static.copy_(q_new)
+        graph.replay()
+        torch.cuda.synchronize()
+        out_e, lse_e = step(q_new)
+        torch.cuda.synchronize()
+        assert torch.equal(out_g, out_e) and torch.equal(lse_g, lse_e)
+
+
 def test_argument_errors():
     fm = _api()
     t = gen.DecodeCase(b=1, s_q=1, s_k=64, h_q=16)

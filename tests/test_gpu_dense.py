@@ -134,6 +134,20 @@ def test_dense_bitwise_determinism():
             assert torch.equal(a, b)
 
 
+def test_dense_deterministic_flag_is_accepted():
+    import flashmla_windows_linux_sm120_b200 as fm
+    c = gen.make_dense_case(gen.DenseCase(b=1, mean_sq=130, mean_sk=130, varlen=False, h=2, h_k=2, d=128, dv=128, causal=True))
+    cu = c["cu_q"].cuda()
+    res = []
+    for det in (False, True):
+        q, k, v = (c[n].cuda().requires_grad_() for n in ("q", "k", "v"))
+        out, _ = fm.flash_attn_varlen_func(q, k, v, cu, cu, c["max_q"], c["max_k"], softmax_scale=c["scale"], causal=True,
+                                           deterministic=det)
+        out.backward(c["d_out"].cuda())
+        res.append((out.detach(), q.grad, k.grad, v.grad))
+    assert all(torch.equal(a, b) for a, b in zip(*res))
+
+
 def test_dense_bwd_rejects_gqa():
     c = gen.make_dense_case(gen.DenseCase(b=1, mean_sq=64, mean_sk=64, varlen=False, h=4, h_k=2, d=128, dv=128, causal=False))
     with pytest.raises(ValueError):
