@@ -10,12 +10,14 @@ from .flash_mla_interface import (  # noqa: F401
     flash_attn_varlen_qkvpacked_func,
     flash_mla_sparse_fwd,
     flash_mla_with_kvcache,
+    flash_mla_sparse_decode_logical_indices,
     get_mla_metadata,
 )
 
 __all__ = [
     "get_mla_metadata",
     "flash_mla_with_kvcache",
+    "flash_mla_sparse_decode_logical_indices",
     "flash_attn_varlen_func",
     "flash_attn_varlen_qkvpacked_func",
     "flash_attn_varlen_kvpacked_func",

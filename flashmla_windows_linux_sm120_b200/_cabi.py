@@ -28,6 +28,7 @@ class DecodeParams(C.Structure):
         ("out", vp), ("o_stride_b", i64), ("o_stride_s", i64), ("o_stride_h", i64),
         ("softmax_lse", vp), ("lse_accum", vp), ("o_accum", vp),
         ("profile_event_begin", vp), ("profile_event_end", vp),
+        ("indices_logical", i32),
     ]
 
 

@@ -186,6 +186,7 @@ static int decode_impl(const fmla_decode_params* P, const fmla_peer_push* push, 
   k.block_table = a.block_table; k.block_table_stride_b = a.block_table_stride_b;
   k.seqlens_k = a.seqlens_k;
   k.indices = a.indices; k.indices_stride_b = a.indices_stride_b; k.indices_stride_s = a.indices_stride_s;
+  k.indices_logical = (sparse && a.indices_logical) ? 1 : 0;
   k.tile_scheduler_metadata = a.tile_scheduler_metadata; k.num_sm_parts = a.num_sm_parts; k.num_splits = a.num_splits;
   k.out = a.out; k.o_stride_b = a.o_stride_b; k.o_stride_s = a.o_stride_s; k.o_stride_h = a.o_stride_h;
   k.softmax_lse = a.softmax_lse; k.lse_accum = a.lse_accum; k.o_accum = a.o_accum;

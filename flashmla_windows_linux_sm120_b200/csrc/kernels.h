@@ -35,6 +35,7 @@ struct DecodeKernelParams {
   // merge of the local splits is pushed, as a normalised fp32 partial, into slot `push_slot` of each
   // destination's partial buffers (peer-mapped device memory), followed by a flag store.
   int is_f16;                  // q, cache and out are fp16 instead of bf16 (dense decode only)
+  int indices_logical;         // sparse decode: indices are token positions, mapped through block_table in the kernel
   int force_partial;
   int push_slot, push_num_dst;
   float* push_o[8];            // [num_slots][b * h_k * rows][512]

@@ -349,6 +349,13 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
       int my_slot = -1;             // lanes 0..7: slot of row 8*gw + lane of the fetched block
       auto fetch = [&](const Work& r, int blk) {
         my_slot = __ldg(r.idx + blk * 64 + gw * 8 + (lane & 7));
+        if (p.indices_logical) {
+          // token position of the request -> physical slot through its block table
+          const int pos = my_slot;
+          my_slot = -1;
+          if (pos >= 0 && pos < __ldg(p.seqlens_k + r.batch))
+            my_slot = __ldg(p.block_table + r.batch * p.block_table_stride_b + (pos >> 6)) * 64 + (pos & 63);
+        }
         if (my_slot < 0 || my_slot >= p.num_blocks * 64) my_slot = -1;
 #pragma unroll
         for (int rr = 0; rr < 8; ++rr) {

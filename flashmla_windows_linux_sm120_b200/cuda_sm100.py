@@ -57,7 +57,8 @@ def get_mla_decoding_metadata(seqlens_k: torch.Tensor, num_q_tokens_per_head_k: 
 def fwd_kvcache_mla(q: torch.Tensor, kcache: torch.Tensor, head_size_v: int, seqlens_k: torch.Tensor,
                     block_table: torch.Tensor, softmax_scale: float, is_causal: bool,
                     tile_scheduler_metadata: torch.Tensor, num_splits: torch.Tensor, is_fp8: bool = False,
-                    indices: Optional[torch.Tensor] = None, profile_events=None) -> List[torch.Tensor]:
+                    indices: Optional[torch.Tensor] = None, profile_events=None,
+                    indices_logical: bool = False) -> List[torch.Tensor]:
     """csrc/pybind.cpp:430-720.  Returns [out [b,s_q,h_q,dv] (q dtype), softmax_lse [b,h_q,s_q] fp32].
     profile_events: optional (begin, end) pair of torch.cuda.Event(enable_timing=True) recorded around the
     attention kernel alone (they must have been recorded once already so that their handles exist)."""
@@ -126,6 +127,7 @@ def fwd_kvcache_mla(q: torch.Tensor, kcache: torch.Tensor, head_size_v: int, seq
         p.seqlens_k = seqlens_k.data_ptr()
         if sparse:
             p.indices, p.indices_stride_b, p.indices_stride_s = indices.data_ptr(), indices.stride(0), indices.stride(1)
+            p.indices_logical = int(bool(indices_logical))
         p.tile_scheduler_metadata, p.num_sm_parts = tile_scheduler_metadata.data_ptr(), num_sm_parts
         p.num_splits = num_splits.data_ptr()
         p.out, p.o_stride_b, p.o_stride_s, p.o_stride_h = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)

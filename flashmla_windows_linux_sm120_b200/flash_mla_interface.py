@@ -52,6 +52,23 @@ def flash_mla_with_kvcache(q: torch.Tensor, k_cache: torch.Tensor, block_table: 
     return out, lse
 
 
+def flash_mla_sparse_decode_logical_indices(q: torch.Tensor, k_cache: torch.Tensor, block_table: torch.Tensor,
+                                            cache_seqlens: torch.Tensor, head_dim_v: int,
+                                            tile_scheduler_metadata: torch.Tensor, num_splits: torch.Tensor,
+                                            indices: torch.Tensor, softmax_scale: Optional[float] = None
+                                            ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Sparse FP8 decode whose `indices` (b, s_q, topk) hold token POSITIONS of each request (what a top-k indexer
+    produces; < 0 or >= cache_seqlens[b] = padding) instead of physical slots: the kernel maps them through
+    block_table itself, which saves the caller's remap (README.md:176 of the reference).  No counterpart in the
+    reference API; everything else as flash_mla_with_kvcache(..., is_fp8_kvcache=True)."""
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** (-0.5)
+    out, lse = flash_mla_cuda.fwd_kvcache_mla(q, k_cache, head_dim_v, cache_seqlens, block_table, softmax_scale,
+                                              False, tile_scheduler_metadata, num_splits, True, indices,
+                                              indices_logical=True)
+    return out, lse
+
+
 def flash_mla_sparse_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: float,
                          d_v: int = 512) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Sparse attention prefill (reference: flash_mla_interface.py:315-342).

@@ -120,6 +120,12 @@ typedef struct fmla_decode_params {
    * the attention kernel (the combine kernel follows the second); NULL = off. */
   void* profile_event_begin;
   void* profile_event_end;
+
+  /* sparse decode only: when non-zero, `indices` hold LOGICAL token positions of the request (what a top-k
+   * indexer produces); the kernel maps them through block_table itself (position p -> slot
+   * block_table[b][p / 64] * 64 + p % 64; p < 0 or p >= seqlens_k[b] = padding).  No counterpart in the
+   * reference, whose callers remap to physical slots first (README.md:176). */
+  int32_t indices_logical;
 } fmla_decode_params;
 
 /* Bytes of lse_accum and o_accum for a problem (host-side arithmetic only). */

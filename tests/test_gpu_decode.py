@@ -132,6 +132,22 @@ def test_sparse_fp8_decode(b, s_q, s_k, topk, h_q, invalid):
     U.assert_out_lse(out, lse, ref_out, ref_lse)
 
 
+def test_sparse_fp8_decode_logical_indices():
+    """Token positions mapped through the block table inside the kernel give exactly what the caller-side remap
+    to physical slots gives."""
+    fm = _api()
+    t = gen.DecodeCase(b=5, s_q=2, s_k=700, is_varlen=True, topk=128, h_q=128)
+    d = gen.make_decode_case(t)
+    kq = quant.quantize_k_cache(d.blocked_k, t.dv, 128)
+    out_p, lse_p = _run_sparse(d, t, kq)
+    lens = d.cache_seqlens.cuda()
+    md, ns = fm.get_mla_metadata(lens, t.s_q * t.h_q, 1, t.h_q, True, t.topk)
+    out_l, lse_l = fm.flash_mla_sparse_decode_logical_indices(d.q.cuda(), kq.cuda(), d.block_table.cuda(), lens, t.dv, md, ns,
+                                                              d.abs_indices.cuda())
+    torch.cuda.synchronize()
+    assert torch.equal(out_l.cpu(), out_p) and torch.equal(lse_l.cpu(), lse_p)
+
+
 @pytest.mark.parametrize("name", ["decode_sparse_fp8", "decode_sparse_fp8_pad"])
 def test_sparse_fp8_decode_golden(name):
     fm = _api()
