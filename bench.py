@@ -32,7 +32,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 # dram__bytes_read + dram__bytes_write per launch of the dominant kernel, from the committed ncu capture
-# (profiles/mla_tc_kernel_dense__dense_decode_b128_sq1.md)
+# of this kernel on this workload (summary committed under profiles/)
 TRAFFIC_BYTES = {"dense_decode": 708.7e6}
 
 FALLBACK_HBM_GBS = 6650.0
@@ -106,7 +106,7 @@ class ClockSampler:
 # workloads
 # ---------------------------------------------------------------------------------------------
 class DenseDecode:
-    """BASELINE config 2: dense BF16 MLA decode at the DeepSeek-V3 shape."""
+    """Dense BF16 MLA decode at the DeepSeek-V3 shape."""
     metric, unit, dtype = "dense_bf16_mla_decode_bandwidth", "GB/s", "bf16"
     bound = "hbm"
     kernel_name = "mla_tc_kernel<kDense>"
@@ -241,7 +241,7 @@ class DenseDecode:
 
 
 class SparseDecode:
-    """BASELINE config 3: sparse FP8 MLA decode, batch 64, top-k 2048 of 32768 cached tokens."""
+    """Sparse FP8 MLA decode, batch 64, top-k 2048 of 32768 cached tokens."""
     metric, unit, dtype = "sparse_fp8_mla_decode_tflops", "TFLOP/s", "bf16 (fp8 e4m3 cache)"
     bound = "tensor"
     kernel_name = "mla_tc_kernel<kSparseDecode>"
@@ -292,7 +292,7 @@ class SparseDecode:
 
 
 class SparsePrefill:
-    """BASELINE config 4: sparse MLA prefill forward, s_q 4096, s_kv 32768, top-k 2048 (causally restricted)."""
+    """Sparse MLA prefill forward, s_q 4096, s_kv 32768, top-k 2048 (causally restricted)."""
     metric, unit, dtype = "sparse_mla_prefill_fwd_tflops", "TFLOP/s", "bf16"
     bound = "tensor"
     kernel_name = "mla_tc_kernel<kSparsePrefill>"
@@ -329,7 +329,7 @@ class SparsePrefill:
 
 
 class DenseFwdBwd:
-    """BASELINE config 5a: dense causal varlen MHA forward + backward, h 128, d 192/128, 8 sequences U[1024,8192]."""
+    """Dense causal varlen MHA forward + backward, h 128, d 192/128, 8 sequences U[1024,8192]."""
     metric, unit, dtype = "dense_mha_varlen_fwd_bwd_tflops", "TFLOP/s", "bf16"
     bound = "tensor"
     kernel_name = "dense_fwd_tc_kernel<192> + dense_bwd_*"
@@ -374,7 +374,7 @@ class DenseFwdBwd:
 
 
 class DenseFwd(DenseFwdBwd):
-    """BASELINE config 5a, forward only (the reference quotes forward and backward separately)."""
+    """The same workload, forward only (the reference quotes forward and backward separately)."""
     metric = "dense_mha_varlen_fwd_tflops"
     kernel_name = "dense_fwd_tc_kernel<192>"
     launches_per_step = 1
