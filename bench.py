@@ -409,6 +409,13 @@ def dist_env():
     return rank, world, local
 
 
+def use_all_host_threads():
+    """The launcher of multi-process runs sets OMP_NUM_THREADS=1; the CPU legs use every core they can get."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def time_cpu(run, steps, warmup):
     for _ in range(warmup):
         run()
@@ -428,6 +435,7 @@ def run_reference(args, wl):
         print(json.dumps({"impl": "reference", "unavailable": "no CPU sample is defined for this workload; the default workload has one"}))
         return
     wl.make_host(args.seed)
+    use_all_host_threads()
     run, nbytes, sample = wl.cpu_sample()
     steps = max(1, min(args.steps, 5))
     warm = max(1, min(args.warmup, 1))
@@ -551,6 +559,7 @@ def main():
                     "kernel_ms": ms_per_step, "algorithmic_flops_per_launch": wl.alg_flops(), "traffic": None}
         cpu = None
         if not args.no_cpu_baseline and hasattr(wl, "cpu_sample"):
+            use_all_host_threads()
             run, cbytes, sample = wl.cpu_sample()
             sec = time_cpu(run, 3, 1)
             cpu = {"value": cbytes / sec / 1e9, "unit": wl.unit, "cores": torch.get_num_threads(), "kind": "port",
