@@ -73,6 +73,23 @@ def test_dense_decode_fp16(b, s_q, s_k, varlen, causal, h_q, h_kv):
     U.assert_out_lse(out, lse, ref_out, ref_lse)
 
 
+@pytest.mark.parametrize("seed", range(10))
+def test_dense_decode_random_shapes(seed):
+    """Seeded random shapes: batch, queries per request, heads, kv heads, lengths (some zero), causal or not."""
+    import random
+    rng = random.Random(1000 + seed)
+    h_kv = rng.choice([1, 1, 2])
+    h_q = rng.choice([16, 64, 128]) * h_kv if h_kv == 2 else rng.choice([16, 64, 128])
+    t = gen.DecodeCase(b=rng.randint(1, 9), s_q=rng.choice([1, 1, 2, 3]), s_k=rng.choice([30, 200, 700, 2300]),
+                       is_varlen=True, is_causal=rng.random() < 0.5, h_q=min(h_q, 128), h_kv=h_kv,
+                       zero_seqlen=rng.random() < 0.3, seed=seed)
+    d = gen.make_decode_case(t)
+    out, lse, md, ns = _run_dense(d, t)
+    ref_out, ref_lse = decode.decode_ref(d.cache_seqlens, d.block_table, d.q, d.blocked_k, t.dv, t.is_causal)
+    U.assert_out_lse(out, lse, ref_out, ref_lse)
+    scheduler.check_schedule_invariants(md.tolist(), ns.tolist(), d.cache_seqlens.tolist())
+
+
 def test_dense_decode_zero_length_requests():
     t = gen.DecodeCase(b=16, s_q=2, s_k=500, is_varlen=True, is_causal=True, zero_seqlen=True)
     d = gen.make_decode_case(t)

@@ -59,6 +59,34 @@ def test_dense_fwd_bwd_long(d, causal):
     assert check_is_allclose("dv", dvv, r_dv, **TOL)
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_dense_fwd_bwd_random_lengths(seed):
+    """Seeded random sequence lengths including single tokens, key counts below and above a block, and (non-causal)
+    more queries than keys."""
+    import random
+    rng = random.Random(2000 + seed)
+    causal = rng.random() < 0.6
+    b = rng.randint(1, 5)
+    sq = [rng.choice([1, 7, 64, 127, 128, 129, 255, 300, 513]) for _ in range(b)]
+    sk = [max(q if causal else 1, rng.choice([1, 5, 63, 64, 65, 128, 200, 257, 640])) for q in sq]
+    d = rng.choice([192, 128])
+    cu_q = torch.tensor([0] + sq, dtype=torch.int32).cumsum(0).to(torch.int32)
+    cu_k = torch.tensor([0] + sk, dtype=torch.int32).cumsum(0).to(torch.int32)
+    g = torch.Generator().manual_seed(seed)
+    mk = lambda *shape: (torch.randn(*shape, generator=g) / 10).to(torch.bfloat16)
+    h = 2
+    c = dict(q=mk(sum(sq), h, d), k=mk(sum(sk), h, d), v=mk(sum(sk), h, 128), d_out=mk(sum(sq), h, 128), cu_q=cu_q, cu_k=cu_k,
+             max_q=max(sq), max_k=max(sk), scale=(d + 100) ** -0.5)
+    out, lse, (dq, dk, dvv) = _run(c, causal, True)
+    r_out, r_lse, r_dq, r_dk, r_dv = dense.dense_fwd_bwd_ref(c["q"], c["k"], c["v"], c["d_out"], c["cu_q"], c["cu_k"],
+                                                             causal, c["scale"])
+    assert check_is_allclose("out", out, r_out, **TOL)
+    assert check_is_allclose("lse", lse, r_lse, **LSE_TOL)
+    assert check_is_allclose("dq", dq, r_dq, **TOL)
+    assert check_is_allclose("dk", dk, r_dk, **TOL)
+    assert check_is_allclose("dv", dvv, r_dv, **TOL)
+
+
 @pytest.mark.parametrize("causal", [False, True])
 def test_dense_neighbour_sequence_does_not_leak(causal):
     """A tile that overhangs the end of its sequence reads rows of the next one.  Non-finite values there
@@ -104,6 +132,20 @@ def test_dense_packed_inputs_are_read_in_place():
     out_k.backward(d_out)
     assert torch.equal(out_k, out) and torch.equal(lse_k, lse)
     assert torch.equal(qk.grad, qs.grad) and torch.equal(kv.grad[..., :192], ks.grad) and torch.equal(kv.grad[..., 192:], vs.grad)
+
+
+def test_dense_fwd_causal_more_queries_than_keys():
+    """Bottom-right aligned causal mask with s_q > s_k: the first s_q - s_k queries see no key: O = 0, lse = -inf."""
+    torch.manual_seed(3)
+    sq, sk, h, d = 300, 130, 2, 192
+    mk = lambda *shape: (torch.randn(*shape) / 10).to(torch.bfloat16)
+    c = dict(q=mk(sq, h, d), k=mk(sk, h, d), v=mk(sk, h, 128), d_out=mk(sq, h, 128), cu_q=torch.tensor([0, sq], dtype=torch.int32),
+             cu_k=torch.tensor([0, sk], dtype=torch.int32), max_q=sq, max_k=sk, scale=0.06)
+    out, lse, _ = _run(c, True, False)
+    r_out, r_lse = dense.dense_fwd_ref(c["q"], c["k"], c["v"], c["cu_q"], c["cu_k"], True, c["scale"])
+    assert torch.all(out[:sq - sk] == 0) and torch.all(lse[:sq - sk] == float("-inf"))
+    assert check_is_allclose("out", out, r_out, **TOL)
+    assert check_is_allclose("lse", lse[sq - sk:], r_lse[sq - sk:], **LSE_TOL)
 
 
 def test_dense_fwd_gqa_32_over_4():
