@@ -100,10 +100,12 @@ template <int MODE>
 __device__ __forceinline__ Tile make_tile(const TcParams& P) {
   Tile t;
   if constexpr (MODE == kSparsePrefill) {
+    // persistent over query tokens: this CTA takes tokens blockIdx.y, blockIdx.y + gridDim.y, ... so that the
+    // Q load and the output stores of one token overlap with the blocks of its neighbours
     t.hb = blockIdx.x; t.sq = blockIdx.y; t.kh = 0;
     t.head0 = t.hb * 64; t.nvalid = 64;
     t.begin_idx = t.end_idx = 0; t.begin_block = 0; t.end_block = P.sp.topk / 64; t.begin_split = 0;
-    t.n_work = 1;
+    t.n_work = (P.sp.s_q - static_cast<int>(blockIdx.y) + static_cast<int>(gridDim.y) - 1) / static_cast<int>(gridDim.y);
   } else {
     const DecodeKernelParams& p = P.d;
     int part;
@@ -127,11 +129,11 @@ template <int MODE>
 __device__ __forceinline__ Work get_work(const TcParams& P, const Tile& t, int i) {
   Work w;
   if constexpr (MODE == kSparsePrefill) {
-    w.batch = t.sq;
+    w.batch = t.sq + i * static_cast<int>(gridDim.y);          // the query token
     w.blk_lo = 0; w.blk_hi = P.sp.topk / 64;
     w.seqlen = P.sp.topk; w.border = P.sp.topk;
     w.split_slot = 0; w.no_split = true;
-    w.idx = P.sp.indices + (int64_t)t.sq * P.sp.indices_stride_s;
+    w.idx = P.sp.indices + (int64_t)w.batch * P.sp.indices_stride_s;
   } else {
     const DecodeKernelParams& p = P.d;
     const int batch = t.begin_idx + i;
@@ -189,7 +191,7 @@ __device__ __forceinline__ void s_block(uint32_t tmem, uint64_t desc_q, uint64_t
 }
 
 // grid: kDense (s_q*ceil(hq_per_hk/64), h_k, parts), 192 threads;
-//       kSparseDecode (ceil(h_q/64), s_q, parts), 448 threads; kSparsePrefill (h_q/64, s_q), 448 threads
+//       kSparseDecode (ceil(h_q/64), s_q, parts), 448 threads; kSparsePrefill (h_q/64, min(s_q, SMs / (h_q/64))) persistent over the query tokens, 448 threads
 template <int MODE, bool F16>
 __global__ void __launch_bounds__(MODE == kDense ? 192 : 448, 1)
 mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtensorMap tmap_q,
@@ -261,7 +263,7 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
         tc::mbar_arrive_expect_tx(bar(Q_FULL), kTileBytes);
 #pragma unroll
         for (int c = 0; c < 9; ++c)
-          tc::tma_load_4d(sQ + c * kChunkBytes, &tmap_q, c * 64, tile.head0, tile.sq, MODE == kSparsePrefill ? 0 : r.batch, bar(Q_FULL));
+          tc::tma_load_4d(sQ + c * kChunkBytes, &tmap_q, c * 64, tile.head0, MODE == kSparsePrefill ? r.batch : tile.sq, MODE == kSparsePrefill ? 0 : r.batch, bar(Q_FULL));
         if constexpr (MODE == kDense) {
           const int* bt = p.block_table + r.batch * p.block_table_stride_b;
           // pages kPrefetchDist steps ahead are pulled into L2 while the two shared-memory stages are
@@ -663,7 +665,7 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
       float* o_part = nullptr;
       int64_t part_row = 0;
       if constexpr (MODE == kSparsePrefill) {
-        o_final = reinterpret_cast<__nv_bfloat16*>(P.sp.out) + ((int64_t)tile.sq * P.sp.h_q + head) * 512;
+        o_final = reinterpret_cast<__nv_bfloat16*>(P.sp.out) + ((int64_t)r.batch * P.sp.h_q + head) * 512;
       } else {
         const int q_seq_per_hk = p.s_q * p.hq_per_hk;
         const int row_in_group = tile.sq * p.hq_per_hk + tile.hb * 64 + r_row;   // regrouped row index within the kv head
@@ -710,7 +712,7 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
       }
       if (row_ok && th == 0) {
         if constexpr (MODE == kSparsePrefill) {
-          const int64_t o = (int64_t)tile.sq * P.sp.h_q + head;
+          const int64_t o = (int64_t)r.batch * P.sp.h_q + head;
           P.sp.max_logits[o] = inv == 0.f ? neg_inf() : m_run;
           P.sp.lse[o] = inv == 0.f ? neg_inf() : log2f(l) + m_used;
         } else if (r.no_split) {
@@ -793,7 +795,12 @@ cudaError_t launch_sparse_prefill_tc(const SparsePrefillKernelParams& sp, cudaSt
   CUtensorMap tq;
   // q [s_q][h_q][576] as (col, head, token, 1)
   if (!make_map_4d(&tq, sp.q, sp.h_q, sp.s_q, 1, sp.q_stride_h, sp.q_stride_s, sp.q_stride_s * sp.s_q, 64, 1)) return cudaErrorInvalidValue;
-  return launch_tc<kSparsePrefill>(P, tq, tq, dim3(sp.h_q / 64, sp.s_q, 1), stream);
+  // one CTA per SM (and head tile) walks the query tokens
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
+  const int n_hb = sp.h_q / 64;
+  const int lanes = max(1, min(sp.s_q, sms / n_hb));
+  return launch_tc<kSparsePrefill>(P, tq, tq, dim3(n_hb, lanes, 1), stream);
 }
 
 #ifdef FMLA_TRACE
