@@ -564,25 +564,21 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
         tc::mbar_arrive(bar(S_EMPTY0 + st));
         if (tid == 0) FMLA_TRACE_AT(g, 7);
 
-        float s[32];
-        float mx = neg_inf();
         if constexpr (MODE == kDense) {
           const int tok0 = (r.blk_lo + j) * 64 + th * 32;
           if (tok0 + 32 > r.border) vbits = tok0 >= r.border ? 0u : (0xffffffffu >> (32 - (r.border - tok0)));
         }
+        // masked logits become -inf (a select: they may hold anything); the maximum is taken over the raw
+        // logits in four independent chains and scaled once (the scale is positive)
         if (vbits != 0xffffffffu) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            s[i] = ((vbits >> i) & 1u) ? __uint_as_float(sv[i]) * scale_log2 : neg_inf();
-            mx = fmaxf(mx, s[i]);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            s[i] = __uint_as_float(sv[i]) * scale_log2;
-            mx = fmaxf(mx, s[i]);
-          }
+          for (int i = 0; i < 32; ++i)
+            if (!((vbits >> i) & 1u)) sv[i] = 0xff800000u;
         }
+        float mx4[4] = {neg_inf(), neg_inf(), neg_inf(), neg_inf()};
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
         float* xch = sMx + (j & 1) * 128;
         xch[tid] = mx;
         bar_sync(1, 128);
@@ -623,15 +619,16 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
           tc::tc_fence_before();
         }
         if (tid == 0) FMLA_TRACE_AT(g, 10);
-        float rs = 0.f;
+        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = exp2f(s[2 * i] - m_used), p1 = exp2f(s[2 * i + 1] - m_used);
-          rs += p0 + p1;
+          const float p0 = exp2f(fmaf(__uint_as_float(sv[2 * i]), scale_log2, -m_used));
+          const float p1 = exp2f(fmaf(__uint_as_float(sv[2 * i + 1]), scale_log2, -m_used));
+          rs4[i & 3] += p0 + p1;
           pk[i] = pack_16x2<F16>(p0, p1);
         }
-        l_part += rs;
+        l_part += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
         if (!pv_done && !tc::mbar_wait(bar(P_EMPTY), (g & 1) ^ 1, status, 9)) *sAbort = 1;
         if (tid == 0) FMLA_TRACE_AT(g, 9);
         // P[row][th*32 .. +32) -> K-major 128B-swizzled A operand: 16-byte chunk (th*4 + q) ^ (row & 7)
