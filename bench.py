@@ -2,17 +2,26 @@
 """Benchmark of the MLA attention hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+                    [--small] [--no-extras] [--no-cpu-baseline]
 
-One "step" = one pass of the hot path (the public API call) over one batch of
-seeded synthetic input.  Default workload: dense BF16 MLA decode at the
-DeepSeek-V3 shape (batch 128 per GPU, s_q 1, 128 heads, d 576/512, sequence
-lengths uniform in [3072, 5120], paged cache with a shuffled block table).
-Prints ONE JSON line (rank 0).  Timing: CUDA events on the launching stream, W
-warm-up steps, K timed steps bracketed by barrier + synchronize, max over ranks.
-The working set (~600 MB) is several times the 126 MB L2, so no flush is needed.
+One "step" = one pass of the hot path (the public API call) over one batch of seeded synthetic input.
+Default workload: dense BF16 MLA decode at the DeepSeek-V3 shape (batch 128 per GPU, s_q 1, 128 heads,
+d 576/512, sequence lengths uniform in [3072, 5120], paged cache with a shuffled block table).
+Prints ONE JSON line (rank 0).  Timing: CUDA events on the launching stream, W warm-up steps, K timed
+steps bracketed by barrier + synchronize, max over ranks.  Every working set is several times the 126 MB
+L2 (or, for the sparse prefill, L2-resident by the nature of the workload), so no flush is needed.
 
-`--impl reference` times the reference's CPU algorithm for the same workload
-(the oracle port of its torch path) on the host cores, on a bounded sample.
+The line of the default run also carries, outside the headline timing:
+  parity_checked  a sample of the step's outputs compared with the CPU oracle after the timed region
+  sustained       the same step repeated for at least one second (clocks sampled over that stretch)
+  workloads       the other configurations (sparse FP8 decode, sparse prefill, dense MHA forward and
+                  forward+backward, dense decode at s_q = 2, the KV-sharded 1 M-token decode), each for
+                  >= 20 steps with its own roofline fraction, parity sample and clocks
+  e2e.copy_only   the same host<->device copies without the kernel (what the host fabric alone allows)
+
+`--impl reference` times the reference's CPU algorithm for the same workload (the oracle port of its torch
+path) on the host cores, on a bounded sample.  `--small` shrinks every workload to a few hundred MB for
+profiler captures.
 """
 from __future__ import annotations
 
@@ -24,6 +33,7 @@ import statistics
 import sys
 import threading
 import time
+import traceback
 
 import torch
 
@@ -31,9 +41,12 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# dram__bytes_read + dram__bytes_write per launch of the dominant kernel, from the committed ncu capture
-# of this kernel on this workload (summary committed under profiles/)
-TRAFFIC_BYTES = {"dense_decode": 708.7e6}
+# dram__bytes_read + dram__bytes_write per launch of the dominant kernel, from ncu captures of that kernel
+# (summaries under profiles/).  "full" = captured on the full workload; otherwise bytes per unit of a small
+# case, scaled by the units one launch of the benchmark workload processes (traffic grows in proportion).
+TRAFFIC = {
+    "dense_decode": {"per_token": 708.7e6 / 526851, "unit": "cached token", "source": "full-size capture, 1 pass set"},
+}
 
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
@@ -53,13 +66,13 @@ def measured_peaks():
 
 
 # ---------------------------------------------------------------------------------------------
-# clocks: sampled in-process through NVML (read-only) while the timed region runs
+# clocks: sampled in-process through NVML (read-only) while a timed region runs
 # ---------------------------------------------------------------------------------------------
 class ClockSampler:
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
                0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x10: "sync_boost"}
 
-    def __init__(self, index: int, period_s: float = 0.004):
+    def __init__(self, index: int, period_s: float = 0.002):
         self.samples, self.reasons, self.period = [], set(), period_s
         self.max_mhz = None
         self._stop = threading.Event()
@@ -93,6 +106,7 @@ class ClockSampler:
         if self.nv is not None:
             self._thr = threading.Thread(target=self._loop, daemon=True)
             self._thr.start()
+        return self
 
     def stop(self):
         if self._thr is not None:
@@ -102,18 +116,114 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def _errs(out, ref_out, lse=None, ref_lse=None):
+    from oracle.check import max_abs_diff
+    d = {"out_max_abs": max_abs_diff(out, ref_out), "out_bound": 2e-3 * max(1.0, float(ref_out.float().abs().max()))}
+    if lse is not None:
+        d["lse_max_abs"] = max_abs_diff(lse, ref_lse)
+    return d
+
+
 # ---------------------------------------------------------------------------------------------
 # workloads
 # ---------------------------------------------------------------------------------------------
-class DenseDecode:
+class Workload:
+    """One benchmarked configuration.  `units` of work are bytes for the HBM-bound decode and FLOPs for the
+    others (the reference's own formulas)."""
+    scaling = "weak"
+    e2e_buffers = 1          # sets of device input / host output buffers of the end-to-end loop
+    e2e_max_steps = 5
+    world = 1
+    rank = 0
+    sharding = "requests sharded, no collective"
+
+    # ---- end to end through the public API: inputs from pinned host memory, results back to pinned host memory.
+    # With two buffer sets the copies of neighbouring steps overlap with the kernels (three streams).
+    def e2e_begin(self):
+        dev = self.device
+        if not hasattr(self, "_E"):
+            n = self.e2e_buffers
+            E = self._E = argparse.Namespace()
+            E.n = n
+            E.s_in, E.s_cmp, E.s_out = (torch.cuda.Stream(dev) for _ in range(3))
+            E.h_in = {k: (v if v.is_pinned() else v.pin_memory()) for k, v in self.host_inputs().items()}
+            E.d_in = [{k: torch.empty(v.shape, dtype=v.dtype, device=dev) for k, v in E.h_in.items()} for _ in range(n)]
+            E.h_out = [None] * n
+            E.ev_in = [torch.cuda.Event() for _ in range(n)]
+            E.ev_cmp = [torch.cuda.Event() for _ in range(n)]
+            E.ev_out = [torch.cuda.Event() for _ in range(n)]
+            E.keep = [None] * n
+            E.d2h = 0
+        self._E.k = 0
+        main = torch.cuda.current_stream(dev)
+        for st in (self._E.s_in, self._E.s_cmp, self._E.s_out):
+            st.wait_stream(main)
+
+    def step_e2e(self, run_kernel: bool = True):
+        E = self._E
+        i = E.k % E.n
+        E.k += 1
+        later = E.k > E.n
+        with torch.cuda.stream(E.s_in):
+            if later:
+                E.s_in.wait_event(E.ev_cmp[i])       # the step that read this set of inputs
+            for k, v in E.h_in.items():
+                E.d_in[i][k].copy_(v, non_blocking=True)
+            E.ev_in[i].record(E.s_in)
+        with torch.cuda.stream(E.s_cmp):
+            E.s_cmp.wait_event(E.ev_in[i])
+            if later:
+                E.s_cmp.wait_event(E.ev_out[i])      # results of that step have been read back
+            outs = self.run_from(E.d_in[i]) if run_kernel or E.keep[i] is None else E.keep[i]
+            E.ev_cmp[i].record(E.s_cmp)
+        if E.h_out[i] is None:
+            E.h_out[i] = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+            E.d2h = sum(o.numel() * o.element_size() for o in outs)
+        with torch.cuda.stream(E.s_out):
+            E.s_out.wait_event(E.ev_cmp[i])
+            for h, o in zip(E.h_out[i], outs):
+                h.copy_(o, non_blocking=True)
+            E.ev_out[i].record(E.s_out)
+        E.keep[i] = outs
+
+    def e2e_end(self):
+        main = torch.cuda.current_stream(self.device)
+        for st in (self._E.s_in, self._E.s_cmp, self._E.s_out):
+            main.wait_stream(st)
+
+    def e2e_bytes(self):
+        h2d = sum(v.numel() * v.element_size() for v in self._E.h_in.values())
+        return h2d, self._E.d2h
+
+    def release(self):
+        for k in list(self.__dict__):
+            if isinstance(self.__dict__[k], (torch.Tensor, list, dict, argparse.Namespace)):
+                del self.__dict__[k]
+        torch.cuda.empty_cache()
+
+    def imbalance(self):
+        return None
+
+    def traffic(self):
+        return None
+
+
+class DenseDecode(Workload):
     """Dense BF16 MLA decode at the DeepSeek-V3 shape."""
     metric, unit, dtype = "dense_bf16_mla_decode_bandwidth", "GB/s", "bf16"
     bound = "hbm"
     kernel_name = "mla_tc_kernel<kDense>"
     launches_per_step = 2          # split-KV attention + combine
+    e2e_buffers = 2
+    e2e_max_steps = 10 ** 9
 
-    def __init__(self, s_q: int = 1, batch: int = 128, h_q: int = 128):
+    def __init__(self, s_q: int = 1, batch: int = 128, h_q: int = 128, small: bool = False):
+        if small:
+            batch = 16
         self.s_q, self.b, self.h_q = s_q, batch, h_q
+        self.key = "dense_decode" if s_q == 1 else f"dense_decode_sq{s_q}"
+        if s_q > 1:
+            self.metric, self.unit, self.bound = "dense_bf16_mla_decode_tflops", "TFLOP/s", "tensor"
         self.name = f"dense_bf16_decode b={batch}/gpu s_q={s_q} h_q={h_q} h_kv=1 d=576 dv=512 seqlen~U[3072,5120] page=64"
 
     def make_host(self, seed: int):
@@ -130,22 +240,16 @@ class DenseDecode:
             o += n
         self.num_pages = total
 
-    def setup(self, device, seed: int):
+    def setup(self, device, seed: int, rank: int = 0, world: int = 1):
         import flashmla_windows_linux_sm120_b200 as fm
-        self.fm = fm
-        self.make_host(seed)
-        torch.manual_seed(seed)
+        self.fm, self.device, self.rank, self.world = fm, device, rank, world
+        self.make_host(seed + rank)
+        torch.manual_seed(seed + rank)
         self.cache = torch.randn((self.num_pages, 64, 1, 576), dtype=torch.bfloat16, device=device)
         self.q = torch.randn((self.b, self.s_q, self.h_q, 576), dtype=torch.bfloat16, device=device)
         self.d_lens = self.lens.to(device)
         self.d_bt = self.block_table.to(device)
         self.md, self.ns = fm.get_mla_metadata(self.d_lens, self.s_q * self.h_q, 1)
-        self.h_q_pin = self.q.cpu().pin_memory()
-        self.h_bt_pin = self.block_table.pin_memory()
-        self.h_lens_pin = self.lens.pin_memory()
-        self.h_out = torch.empty((self.b, self.s_q, self.h_q, 512), dtype=torch.bfloat16).pin_memory()
-        self.h_lse = torch.empty((self.b, self.h_q, self.s_q), dtype=torch.float32).pin_memory()
-        self.device = device
 
     # reference formulas: tests/test_flash_mla_decoding.py:255-268
     def alg_bytes(self, lens=None):
@@ -156,112 +260,87 @@ class DenseDecode:
         lens = self.lens if lens is None else lens
         return int(self.h_q * self.s_q * 2 * (576 + 512) * int(lens.sum()))
 
+    def traffic(self):
+        return TRAFFIC["dense_decode"]["per_token"] * int(self.lens.sum()) if self.s_q == 1 else None
+
     def step(self, events=None):
         from flashmla_windows_linux_sm120_b200 import cuda_sm100
         return cuda_sm100.fwd_kvcache_mla(self.q, self.cache, 512, self.d_lens, self.d_bt, 576 ** -0.5, True, self.md,
                                           self.ns, False, None, profile_events=events)
 
-    # End to end = the serving loop a user of the API writes: the inputs of a step come from pinned host memory,
-    # the results go back to pinned host memory, and the copies of neighbouring steps overlap with the kernels
-    # (three streams, two sets of buffers).  Every step copies its own inputs and reads its own results.
-    def e2e_begin(self):
-        dev = self.device
-        if not hasattr(self, "_s_in"):
-            self._s_in, self._s_cmp, self._s_out = (torch.cuda.Stream(dev) for _ in range(3))
-            self._d_q = [torch.empty_like(self.q) for _ in range(2)]
-            self._d_bt = [torch.empty_like(self.d_bt) for _ in range(2)]
-            self._d_lens = [torch.empty_like(self.d_lens) for _ in range(2)]
-            self._h_out = [torch.empty_like(self.h_out).pin_memory() for _ in range(2)]
-            self._h_lse = [torch.empty_like(self.h_lse).pin_memory() for _ in range(2)]
-            self._ev_in = [torch.cuda.Event() for _ in range(2)]
-            self._ev_cmp = [torch.cuda.Event() for _ in range(2)]
-            self._ev_out = [torch.cuda.Event() for _ in range(2)]
-            self._keep = [None, None]
-        self._k = 0
-        main = torch.cuda.current_stream(dev)
-        for st in (self._s_in, self._s_cmp, self._s_out):
-            st.wait_stream(main)
+    def host_inputs(self):
+        return {"q": self.q.cpu(), "bt": self.block_table, "lens": self.lens}
 
-    def step_e2e(self):
-        i = self._k & 1
-        self._k += 1
-        with torch.cuda.stream(self._s_in):
-            if self._k > 2:
-                self._s_in.wait_event(self._ev_cmp[i])      # the decode that read this set of inputs two steps ago
-            self._d_q[i].copy_(self.h_q_pin, non_blocking=True)
-            self._d_bt[i].copy_(self.h_bt_pin, non_blocking=True)
-            self._d_lens[i].copy_(self.h_lens_pin, non_blocking=True)
-            self._ev_in[i].record(self._s_in)
-        with torch.cuda.stream(self._s_cmp):
-            self._s_cmp.wait_event(self._ev_in[i])
-            if self._k > 2:
-                # the results of two steps ago are dropped below; whatever reuses their memory on this
-                # stream must come after their read-back
-                self._s_cmp.wait_event(self._ev_out[i])
-            out, lse = self.fm.flash_mla_with_kvcache(self._d_q[i], self.cache, self._d_bt[i], self._d_lens[i], 512,
-                                                      self.md, self.ns, causal=True)
-            self._ev_cmp[i].record(self._s_cmp)
-        with torch.cuda.stream(self._s_out):
-            self._s_out.wait_event(self._ev_cmp[i])
-            self._h_out[i].copy_(out, non_blocking=True)
-            self._h_lse[i].copy_(lse, non_blocking=True)
-            self._ev_out[i].record(self._s_out)
-        self._keep[i] = (out, lse)
+    def run_from(self, d):
+        return self.fm.flash_mla_with_kvcache(d["q"], self.cache, d["bt"], d["lens"], 512, self.md, self.ns, causal=True)
 
-    def e2e_end(self):
-        main = torch.cuda.current_stream(self.device)
-        for st in (self._s_in, self._s_cmp, self._s_out):
-            main.wait_stream(st)
-
-    def e2e_bytes(self):
-        h2d = self.h_q_pin.numel() * 2 + self.h_bt_pin.numel() * 4 + self.h_lens_pin.numel() * 4
-        d2h = self.h_out.numel() * 2 + self.h_lse.numel() * 4
-        return h2d, d2h
-
-    def value_from(self, seconds_per_step, n_gpus_bytes):
-        return n_gpus_bytes / seconds_per_step / 1e9
-
-    def cpu_sample(self, n_req: int = 32):
-        """The reference's CPU torch path on the first n_req requests of this workload."""
+    def parity(self, n_req: int = 16):
+        """Outputs of one more step against the CPU oracle on n_req requests spread over the batch."""
         from oracle import decode
-        lens = self.lens[:n_req]
+        out, lse = self.step()
+        torch.cuda.synchronize()
+        sel = sorted(set(int(round(i * (self.b - 1) / max(n_req - 1, 1))) for i in range(min(n_req, self.b))))
+        lens = self.lens[sel]
         nb = int(((lens + 63) // 64).max())
-        bt = self.block_table[:n_req, :nb].clone()
+        bt = self.block_table[sel, :nb].clone()
         used = torch.unique(bt[bt < self.num_pages])
         remap = torch.full((self.num_pages,), -1, dtype=torch.int64)
         remap[used.long()] = torch.arange(len(used))
         bt = torch.where(bt < self.num_pages, remap[bt.clamp(max=self.num_pages - 1).long()].to(torch.int32), bt)
+        cache = self.cache[used.to(self.device).long()].cpu()
+        r_out, r_lse = decode.decode_ref(lens, bt, self.q[sel].cpu(), cache, 512, self.s_q > 1)
+        d = _errs(out[sel].cpu(), r_out, lse[sel].cpu(), r_lse)
+        d.update(sample=f"{len(sel)} of {self.b} requests, oracle.decode.decode_ref", ok=bool(d["out_max_abs"] <= d["out_bound"] and d["lse_max_abs"] <= 1e-4))
+        return d
+
+    def cpu_sample(self, n_req: int = 32):
+        """The reference's CPU torch path on n_req requests with the sequence lengths of this workload."""
+        from oracle import decode
+        n_req = min(n_req, self.b)
+        lens = self.lens[:n_req]
+        nblk = (lens + 63) // 64
+        total = int(nblk.sum())
+        bt = torch.full((n_req, int(nblk.max())), 2147480000, dtype=torch.int32)
+        perm = torch.randperm(total, generator=torch.Generator().manual_seed(1), dtype=torch.int32)
+        o = 0
+        for i in range(n_req):
+            bt[i, :int(nblk[i])] = perm[o:o + int(nblk[i])]
+            o += int(nblk[i])
         torch.manual_seed(1)
-        cache = torch.randn((len(used), 64, 1, 576), dtype=torch.bfloat16)
+        cache = torch.randn((total, 64, 1, 576), dtype=torch.bfloat16)
         q = torch.randn((n_req, self.s_q, self.h_q, 576), dtype=torch.bfloat16)
 
         def run():
             return decode.decode_ref(lens, bt, q, cache, 512, self.s_q > 1)
-        return run, self.alg_bytes(lens), f"first {n_req} of {self.b} requests ({int(lens.sum())} tokens), oracle.decode.decode_ref"
+        units = self.alg_bytes(lens) if self.bound == "hbm" else self.alg_flops(lens)
+        return run, units, f"first {n_req} of {self.b} requests ({int(lens.sum())} tokens), oracle.decode.decode_ref"
 
 
-class SparseDecode:
+class SparseDecode(Workload):
     """Sparse FP8 MLA decode, batch 64, top-k 2048 of 32768 cached tokens."""
     metric, unit, dtype = "sparse_fp8_mla_decode_tflops", "TFLOP/s", "bf16 (fp8 e4m3 cache)"
     bound = "tensor"
+    key = "sparse_decode"
     kernel_name = "mla_tc_kernel<kSparseDecode>"
     launches_per_step = 2
 
-    def __init__(self, batch: int = 64, topk: int = 2048, seqlen: int = 32768, h_q: int = 128):
+    def __init__(self, batch: int = 64, topk: int = 2048, seqlen: int = 32768, h_q: int = 128, small: bool = False):
+        if small:
+            batch = 16
         self.b, self.topk, self.seqlen, self.h_q, self.s_q = batch, topk, seqlen, h_q, 1
         self.name = f"sparse_fp8_decode b={batch}/gpu s_q=1 h_q={h_q} topk={topk} seqlen_k={seqlen} 656B/token page=64"
 
     def make_host(self, seed: int):
         pass
 
-    def setup(self, device, seed: int):
+    def setup(self, device, seed: int, rank: int = 0, world: int = 1):
         import flashmla_windows_linux_sm120_b200 as fm
         from flashmla_windows_linux_sm120_b200 import cuda_sm100
-        self.fm = fm
-        torch.manual_seed(seed)
+        self.fm, self.device, self.rank, self.world = fm, device, rank, world
+        torch.manual_seed(seed + rank)
         pages_per = self.seqlen // 64
         npages = self.b * pages_per
-        g = torch.Generator(device="cpu").manual_seed(seed)
+        g = torch.Generator(device="cpu").manual_seed(seed + rank)
         perm = torch.randperm(npages, generator=g, dtype=torch.int32)
         self.block_table = perm.view(self.b, pages_per).to(device)
         self.lens = torch.full((self.b,), self.seqlen, dtype=torch.int32, device=device)
@@ -278,7 +357,6 @@ class SparseDecode:
         self.indices = idx
         self.q = torch.randn((self.b, 1, self.h_q, 576), dtype=torch.bfloat16, device=device)
         self.md, self.ns = fm.get_mla_metadata(self.lens, self.h_q, 1, self.h_q, True, self.topk)
-        self.device = device
 
     def alg_bytes(self):
         return int(self.b * (self.h_q * 576 * 2 + self.topk * 656 + self.h_q * 512 * 2))
@@ -290,30 +368,80 @@ class SparseDecode:
         return self.fm.flash_mla_with_kvcache(self.q, self.cache, self.block_table, self.lens, 512, self.md, self.ns,
                                               is_fp8_kvcache=True, indices=self.indices)
 
+    def host_inputs(self):
+        return {"q": self.q.cpu(), "idx": self.indices.cpu(), "bt": self.block_table.cpu(), "lens": self.lens.cpu()}
 
-class SparsePrefill:
+    def run_from(self, d):
+        return self.fm.flash_mla_with_kvcache(d["q"], self.cache, d["bt"], d["lens"], 512, self.md, self.ns,
+                                              is_fp8_kvcache=True, indices=d["idx"])
+
+    def parity(self, n_req: int = 4):
+        """n_req requests: their 2048 records are fetched, de-quantised by the codec oracle and attended on the CPU."""
+        from oracle import decode, quant
+        out, lse = self.step()
+        torch.cuda.synchronize()
+        sel = sorted(set(int(round(i * (self.b - 1) / max(n_req - 1, 1))) for i in range(min(n_req, self.b))))
+        e_out = e_lse = 0.0
+        bound = 0.0
+        flat = self.cache.view(torch.uint8).view(-1, 656)
+        for i in sel:
+            idx = self.indices[i, 0]
+            rows = flat[idx.clamp(min=0).long()].cpu()                                  # [topk, 656]
+            deq = quant.dequantize_k_cache(rows.view(self.topk // 64, 64, 1, 656))      # [topk/64, 64, 1, 576] bf16
+            local = torch.arange(self.topk, dtype=torch.int32)
+            local[idx.cpu() < 0] = -1
+            r_out, r_lse = decode.decode_sparse_physical_ref(self.q[i:i + 1].cpu(), deq, local.view(1, 1, -1), 512)
+            d = _errs(out[i:i + 1].cpu(), r_out, lse[i:i + 1].cpu(), r_lse)
+            e_out, e_lse, bound = max(e_out, d["out_max_abs"]), max(e_lse, d["lse_max_abs"]), max(bound, d["out_bound"])
+        return {"out_max_abs": e_out, "out_bound": bound, "lse_max_abs": e_lse, "ok": bool(e_out <= bound and e_lse <= 1e-4),
+                "sample": f"{len(sel)} of {self.b} requests, oracle.quant.dequantize_k_cache + oracle.decode.decode_sparse_physical_ref"}
+
+    def cpu_sample(self, n_req: int = 4):
+        from oracle import decode, quant
+        torch.manual_seed(2)
+        kv = torch.randn((n_req * self.topk // 64, 64, 1, 576), dtype=torch.bfloat16)
+        cache = quant.quantize_k_cache(kv)
+        q = torch.randn((n_req, 1, self.h_q, 576), dtype=torch.bfloat16)
+        idx = torch.stack([torch.randperm(self.topk, dtype=torch.int32) + i * self.topk for i in range(n_req)]).view(n_req, 1, -1)
+
+        def run():
+            deq = quant.dequantize_k_cache(cache)
+            return decode.decode_sparse_physical_ref(q, deq, idx, 512)
+        return run, int(n_req * self.h_q * 2 * (576 + 512) * self.topk), f"{n_req} of {self.b} requests, de-quantisation + oracle.decode.decode_sparse_physical_ref"
+
+
+class SparsePrefill(Workload):
     """Sparse MLA prefill forward, s_q 4096, s_kv 32768, top-k 2048 (causally restricted)."""
     metric, unit, dtype = "sparse_mla_prefill_fwd_tflops", "TFLOP/s", "bf16"
     bound = "tensor"
+    key = "sparse_prefill"
     kernel_name = "mla_tc_kernel<kSparsePrefill>"
     launches_per_step = 1
+    scaling = "strong"
+    sharding = "query tokens sharded (kv replicated), no collective"
 
-    def __init__(self, s_q: int = 4096, s_kv: int = 32768, topk: int = 2048, h_q: int = 128):
-        self.s_q, self.s_kv, self.topk, self.h_q, self.b = s_q, s_kv, topk, h_q, 1
-        self.name = f"sparse_prefill_fwd s_q={s_q}/gpu h_q={h_q} s_kv={s_kv} topk={topk} causal-restricted indices"
+    def __init__(self, s_q: int = 4096, s_kv: int = 32768, topk: int = 2048, h_q: int = 128, small: bool = False):
+        if small:
+            s_q = 512
+        self.s_q_total, self.s_kv, self.topk, self.h_q, self.b = s_q, s_kv, topk, h_q, 1
+        self.name = f"sparse_prefill_fwd s_q={s_q} h_q={h_q} s_kv={s_kv} topk={topk} causal-restricted indices"
 
     def make_host(self, seed: int):
         pass
 
-    def setup(self, device, seed: int):
+    def setup(self, device, seed: int, rank: int = 0, world: int = 1):
         import flashmla_windows_linux_sm120_b200 as fm
-        self.fm = fm
-        torch.manual_seed(seed)
+        from flashmla_windows_linux_sm120_b200 import parallel
+        self.fm, self.device, self.rank, self.world = fm, device, rank, world
+        self.lo, self.hi = parallel.shard_query_tokens(self.s_q_total, world)[rank]
+        self.s_q = self.hi - self.lo
+        g = torch.Generator(device=device).manual_seed(seed)            # the same kv on every rank
+        self.kv = torch.randn((self.s_kv, 1, 576), dtype=torch.bfloat16, device=device, generator=g)
+        torch.manual_seed(seed + 1000 + rank)
         self.q = torch.randn((self.s_q, self.h_q, 576), dtype=torch.bfloat16, device=device)
-        self.kv = torch.randn((self.s_kv, 1, 576), dtype=torch.bfloat16, device=device)
         idx = torch.empty((self.s_q, 1, self.topk), dtype=torch.int32, device=device)
-        for t in range(self.s_q):                       # query t sits at position s_kv - s_q + t
-            hi = self.s_kv - self.s_q + t + 1
+        for t in range(self.s_q):                       # query t sits at position s_kv - s_q_total + (lo + t)
+            hi = self.s_kv - self.s_q_total + self.lo + t + 1
             idx[t, 0] = torch.randperm(hi, device=device)[:self.topk].to(torch.int32)
         self.indices = idx
         self.scale = 576 ** -0.5
@@ -327,78 +455,292 @@ class SparsePrefill:
     def step(self, events=None):
         return self.fm.flash_mla_sparse_fwd(self.q, self.kv, self.indices, self.scale)
 
+    def host_inputs(self):
+        return {"q": self.q.cpu(), "idx": self.indices.cpu()}
 
-class DenseFwdBwd:
+    def run_from(self, d):
+        return self.fm.flash_mla_sparse_fwd(d["q"], self.kv, d["idx"], self.scale)
+
+    def parity(self, n_tok: int = 64):
+        """n_tok query tokens incl. the first and the last token that a persistent CTA walks."""
+        from oracle import sparse_prefill
+        from oracle.check import max_abs_diff
+        out, mx, lse = self.step()
+        torch.cuda.synchronize()
+        g = torch.Generator().manual_seed(3)
+        lanes = 74 if self.h_q == 128 else 148
+        base = [0, 1, lanes - 1, lanes, self.s_q - lanes, self.s_q - 1]
+        sel = sorted(set([t for t in base if 0 <= t < self.s_q] + torch.randint(0, self.s_q, (n_tok,), generator=g).tolist()))[:n_tok + 6]
+        r_out, r_mx, r_lse = sparse_prefill.sparse_prefill_ref(self.q[sel].cpu(), self.kv.cpu(), self.indices[sel].cpu(), self.scale)
+        d = _errs(out[sel].cpu(), r_out, lse[sel].cpu(), r_lse)
+        d["max_logits_max_abs"] = max_abs_diff(mx[sel].cpu(), r_mx)
+        lim = 1e-4 * math.log2(math.e)      # base-2 quantities
+        d.update(sample=f"{len(sel)} of {self.s_q} query tokens, oracle.sparse_prefill.sparse_prefill_ref",
+                 ok=bool(d["out_max_abs"] <= d["out_bound"] and d["lse_max_abs"] <= lim and d["max_logits_max_abs"] <= lim))
+        return d
+
+    def cpu_sample(self, n_tok: int = 64):
+        from oracle import sparse_prefill
+        torch.manual_seed(4)
+        q = torch.randn((n_tok, self.h_q, 576), dtype=torch.bfloat16)
+        kv = torch.randn((self.s_kv, 1, 576), dtype=torch.bfloat16)
+        idx = torch.stack([torch.randperm(self.s_kv)[:self.topk].to(torch.int32) for _ in range(n_tok)]).view(n_tok, 1, -1)
+        scale = 576 ** -0.5
+
+        def run():
+            return sparse_prefill.sparse_prefill_ref(q, kv, idx, scale)
+        return run, int(2 * self.h_q * (576 + 512) * self.topk * n_tok), f"{n_tok} of {self.s_q_total} query tokens, oracle.sparse_prefill.sparse_prefill_ref"
+
+
+class DenseFwdBwd(Workload):
     """Dense causal varlen MHA forward + backward, h 128, d 192/128, 8 sequences U[1024,8192]."""
     metric, unit, dtype = "dense_mha_varlen_fwd_bwd_tflops", "TFLOP/s", "bf16"
     bound = "tensor"
+    key = "dense_fwd_bwd"
     kernel_name = "dense_fwd_tc_kernel<192> + dense_bwd_*"
     launches_per_step = 4
+    scaling = "strong"
+    sharding = "sequences sharded (longest first), no collective"
+    backward = True
+    e2e_max_steps = 3
 
-    def __init__(self, nseq: int = 8, h: int = 128):
-        self.nseq, self.h, self.b = nseq, h, nseq
-        self.name = f"dense_mha_varlen fwd+bwd {nseq} seqs/gpu L~U[1024,8192] h={h} d=192/128 causal"
+    def __init__(self, nseq: int = 8, h: int = 128, small: bool = False):
+        self.nseq, self.h, self.b, self.small = nseq, h, nseq, small
+        self.name = f"dense_mha_varlen {'fwd+bwd' if self.backward else 'fwd'} {nseq} seqs L~U[1024,8192] h={h} d=192/128 causal"
 
     def make_host(self, seed: int):
-        pass
-
-    def setup(self, device, seed: int):
-        import flashmla_windows_linux_sm120_b200 as fm
-        self.fm = fm
         g = torch.Generator().manual_seed(seed)
-        lens = torch.randint(1024, 8193, (self.nseq,), generator=g, dtype=torch.int32)
+        self.all_lens = torch.randint(1024, 8193, (self.nseq,), generator=g, dtype=torch.int32)
+        if self.small:
+            self.all_lens = self.all_lens[:2].clamp(max=2048)
+
+    def setup(self, device, seed: int, rank: int = 0, world: int = 1):
+        import flashmla_windows_linux_sm120_b200 as fm
+        from flashmla_windows_linux_sm120_b200 import parallel
+        self.fm, self.device, self.rank, self.world = fm, device, rank, world
+        self.make_host(seed)                                            # the same lengths on every rank
+        mine = parallel.shard_sequences(self.all_lens.tolist(), world)[rank]
+        lens = self.all_lens[mine] if mine else torch.zeros((0,), dtype=torch.int32)
         self.lens = lens
+        self.mine = mine
         cu = torch.cumsum(torch.nn.functional.pad(lens, (1, 0)), 0, dtype=torch.int32)
         T = int(lens.sum())
-        torch.manual_seed(seed)
-        mk = lambda d: torch.randn((T, self.h, d), dtype=torch.bfloat16, device=device).requires_grad_()
+        torch.manual_seed(seed + rank)
+        mk = lambda d: torch.randn((max(T, 1), self.h, d), dtype=torch.bfloat16, device=device)[:T].requires_grad_(self.backward)
         self.q, self.k, self.v = mk(192), mk(192), mk(128)
         self.d_out = torch.randn((T, self.h, 128), dtype=torch.bfloat16, device=device)
         self.cu = cu.to(device)
-        self.max_len = int(lens.max())
+        self.cu_host = cu
+        self.max_len = int(lens.max()) if len(lens) else 0
         self.pairs = int(sum(int(l) * (int(l) + 1) // 2 for l in lens))
+        allp = [int(l) * (int(l) + 1) // 2 for l in self.all_lens]
+        loads = [sum(allp[i] for i in s) for s in parallel.shard_sequences(self.all_lens.tolist(), world)]
+        self._imb = max(loads) / (sum(loads) / world) if sum(loads) else None
+
+    def imbalance(self):
+        return self._imb
 
     def alg_bytes(self):
         T = self.q.shape[0]
-        return int(T * self.h * (192 * 2 * 2 + 128 * 2 * 2) * 2)   # q,k,v,o,do read + dq,dk,dv written (approx.)
+        return int(T * self.h * (192 * 2 * 2 + 128 * 2 * 2) * (2 if self.backward else 1))
 
     def alg_flops(self):
-        return int(self.pairs * self.h * 2 * ((192 + 128) + (3 * 192 + 2 * 128)))
+        f = (192 + 128) + ((3 * 192 + 2 * 128) if self.backward else 0)
+        return int(self.pairs * self.h * 2 * f)
+
+    def _run(self, q, k, v, d_out):
+        if len(self.lens) == 0:
+            return ()
+        if not self.backward:
+            with torch.no_grad():
+                return self.fm.flash_attn_varlen_func(q, k, v, self.cu, self.cu, self.max_len, self.max_len, causal=True)
+        q.grad = k.grad = v.grad = None
+        out, lse = self.fm.flash_attn_varlen_func(q, k, v, self.cu, self.cu, self.max_len, self.max_len, causal=True)
+        out.backward(d_out)
+        return out.detach(), lse, q.grad, k.grad, v.grad
 
     def step(self, events=None):
-        self.q.grad = self.k.grad = self.v.grad = None
-        out, lse = self.fm.flash_attn_varlen_func(self.q, self.k, self.v, self.cu, self.cu, self.max_len, self.max_len,
-                                                  causal=True)
-        out.backward(self.d_out)
-        return out, lse
+        return self._run(self.q, self.k, self.v, self.d_out)
+
+    def host_inputs(self):
+        d = {"q": self.q.detach().cpu(), "k": self.k.detach().cpu(), "v": self.v.detach().cpu()}
+        if self.backward:
+            d["d_out"] = self.d_out.cpu()
+        return d
+
+    def run_from(self, d):
+        if self.backward:
+            for n in ("q", "k", "v"):
+                d[n].requires_grad_(True)
+        return self._run(d["q"], d["k"], d["v"], d.get("d_out"))
+
+    def parity(self, heads=(0, 127)):
+        """Heads `heads` of the shortest and of the longest sequence of this rank against the fp32 autograd oracle."""
+        from oracle import dense
+        from oracle.check import max_abs_diff
+        if len(self.lens) == 0:
+            return {"ok": True, "sample": "no sequence on this rank"}
+        res = self.step()
+        torch.cuda.synchronize()
+        seqs = sorted(set([int(torch.argmin(self.lens)), int(torch.argmax(self.lens))]))
+        hs = [h for h in heads if h < self.h]
+        d = {"out_max_abs": 0.0, "out_bound": 0.0, "lse_max_abs": 0.0}
+        if self.backward:
+            d.update(dq_max_abs=0.0, dk_max_abs=0.0, dv_max_abs=0.0, grad_bound=0.0)
+        for s in seqs:
+            a, b = int(self.cu_host[s]), int(self.cu_host[s + 1])
+            sl = lambda t: t.detach()[a:b][:, hs].float().cpu()
+            cu = torch.tensor([0, b - a], dtype=torch.int32)
+            if self.backward:
+                r = dense.dense_fwd_bwd_ref(sl(self.q), sl(self.k), sl(self.v), sl(self.d_out), cu, cu, True)
+            else:
+                r = dense.dense_fwd_ref(sl(self.q), sl(self.k), sl(self.v), cu, cu, True)
+            e = _errs(sl(res[0]), r[0], res[1][a:b][:, hs].cpu(), r[1])
+            d["out_max_abs"], d["out_bound"] = max(d["out_max_abs"], e["out_max_abs"]), max(d["out_bound"], e["out_bound"])
+            d["lse_max_abs"] = max(d["lse_max_abs"], e["lse_max_abs"])
+            if self.backward:
+                for n, got, ref in (("dq", res[2], r[2]), ("dk", res[3], r[3]), ("dv", res[4], r[4])):
+                    d[n + "_max_abs"] = max(d[n + "_max_abs"], max_abs_diff(sl(got), ref))
+                    d["grad_bound"] = max(d["grad_bound"], 2e-3 * max(1.0, float(ref.abs().max())) * 4)
+        ok = d["out_max_abs"] <= d["out_bound"] and d["lse_max_abs"] <= 1e-4
+        if self.backward:
+            ok = ok and all(d[n + "_max_abs"] <= d["grad_bound"] for n in ("dq", "dk", "dv"))
+        d.update(ok=bool(ok), sample=f"heads {hs} of sequences {[int(self.lens[s]) for s in seqs]} tokens, oracle.dense (fp32 autograd)")
+        return d
+
+    def cpu_sample(self, L: int = 2048, heads: int = 8):
+        from oracle import dense
+        torch.manual_seed(5)
+        mk = lambda d: torch.randn((L, heads, d), dtype=torch.bfloat16)
+        q, k, v, do = mk(192), mk(192), mk(128), mk(128)
+        cu = torch.tensor([0, L], dtype=torch.int32)
+
+        def run():
+            if self.backward:
+                return dense.dense_fwd_bwd_ref(q, k, v, do, cu, cu, True)
+            return dense.dense_fwd_ref(q, k, v, cu, cu, True)
+        f = (192 + 128) + ((3 * 192 + 2 * 128) if self.backward else 0)
+        return run, int(L * (L + 1) // 2 * heads * 2 * f), f"one {L}-token sequence, {heads} of {self.h} heads, oracle.dense (fp32 autograd)"
 
 
 class DenseFwd(DenseFwdBwd):
     """The same workload, forward only (the reference quotes forward and backward separately)."""
     metric = "dense_mha_varlen_fwd_tflops"
+    key = "dense_fwd"
     kernel_name = "dense_fwd_tc_kernel<192>"
     launches_per_step = 1
+    backward = False
 
-    def __init__(self, nseq: int = 8, h: int = 128):
-        super().__init__(nseq, h)
-        self.name = f"dense_mha_varlen fwd {nseq} seqs/gpu L~U[1024,8192] h={h} d=192/128 causal"
+
+class KVShardedDecode(Workload):
+    """One 1 M-token context, batch 1, cache pages sharded along the sequence over the ranks; the per-rank
+    partial outputs are merged through peer memory (NVLink stores + flags).  The NCCL all_gather variant is
+    timed beside it."""
+    metric, unit, dtype = "kv_sharded_decode_bandwidth", "GB/s", "bf16"
+    bound = "hbm"
+    key = "kv_sharded_decode"
+    kernel_name = "mla_tc_kernel<kDense> + push/merge"
+    launches_per_step = 3
+    scaling = "strong"
+    sharding = "KV pages of one context sharded along the sequence; peer-memory merge of O / LSE"
+
+    def __init__(self, seqlen: int = 1 << 20, h_q: int = 128, small: bool = False):
+        if small:
+            seqlen = 1 << 17
+        self.seqlen, self.h_q, self.b = seqlen, h_q, 1
+        self.name = f"kv_sharded_decode b=1 s_q=1 h_q={h_q} seqlen={seqlen} d=576 dv=512"
+
+    def make_host(self, seed: int):
+        pass
+
+    def setup(self, device, seed: int, rank: int = 0, world: int = 1):
+        import flashmla_windows_linux_sm120_b200 as fm
+        from flashmla_windows_linux_sm120_b200 import parallel
+        self.fm, self.device, self.rank, self.world, self.parallel = fm, device, rank, world, parallel
+        lo, hi = parallel.shard_kv_pages(self.seqlen, world)[rank]
+        self.n_local = hi - lo
+        npages = max((self.n_local + 63) // 64, 1)
+        g = torch.Generator(device="cpu").manual_seed(seed)             # the same q on every rank
+        self.q = torch.randn((1, 1, self.h_q, 576), generator=g).to(torch.bfloat16).to(device)
+        torch.manual_seed(seed + 100 + rank)
+        self.cache = torch.randn((npages, 64, 1, 576), dtype=torch.bfloat16, device=device)
+        self.bt = torch.randperm(npages, device=device).to(torch.int32).view(1, npages)
+        self.lens = torch.tensor([self.n_local], dtype=torch.int32, device=device)
+        self.nccl_ms = None
+        if world > 1:
+            self.dec = parallel.KVShardedDecode(1, self.h_q, device, transport="peer")
+            self.dec_nccl = parallel.KVShardedDecode(1, self.h_q, device, transport="nccl")
+        else:
+            self.md, self.ns = fm.get_mla_metadata(self.lens, self.h_q, 1)
+
+    def alg_bytes(self):
+        return int(self.n_local * 1152 + (self.h_q * 576 * 2 + self.h_q * 512 * 2) / self.world)
 
     def alg_flops(self):
-        return int(self.pairs * self.h * 2 * (192 + 128))
+        return int(self.h_q * 2 * (576 + 512) * self.n_local)
 
     def step(self, events=None):
-        with torch.no_grad():
-            return self.fm.flash_attn_varlen_func(self.q, self.k, self.v, self.cu, self.cu, self.max_len, self.max_len, causal=True)
+        if self.world > 1:
+            return self.dec(self.q, self.cache, self.bt, self.lens)
+        return self.fm.flash_mla_with_kvcache(self.q, self.cache, self.bt, self.lens, 512, self.md, self.ns)
+
+    def step_nccl(self):
+        return self.dec_nccl(self.q, self.cache, self.bt, self.lens)
+
+    def parity(self, heads: int = 8):
+        """The merged result for the first `heads` heads against the CPU oracle over the whole context."""
+        import torch.distributed as dist
+        from oracle import decode
+        out, lse = self.step()
+        torch.cuda.synchronize()
+        kv_local = self.cache[self.bt[0].long()].reshape(-1, 576)[:self.n_local]
+        if self.world > 1:
+            n_max = (self.seqlen // 64 // self.world + 1) * 64
+            pad = torch.zeros((n_max, 576), dtype=torch.bfloat16, device=self.device)
+            pad[:self.n_local] = kv_local
+            allkv = torch.empty((self.world, n_max, 576), dtype=torch.bfloat16, device=self.device)
+            dist.all_gather_into_tensor(allkv, pad)
+            sizes = [b - a for a, b in self.parallel.shard_kv_pages(self.seqlen, self.world)]
+            kv = torch.cat([allkv[r, :sizes[r]] for r in range(self.world)]).cpu()
+        else:
+            kv = kv_local.cpu()
+        if self.rank != 0:
+            return {"ok": True}
+        L = kv.shape[0]
+        padn = (-L) % 64
+        blocked = torch.cat([kv, torch.zeros(padn, 576, dtype=kv.dtype)]).view(-1, 64, 1, 576)
+        r_out, r_lse = decode.decode_ref(torch.tensor([L], dtype=torch.int32), torch.arange(blocked.shape[0], dtype=torch.int32).view(1, -1),
+                                         self.q[:, :, :heads].cpu(), blocked, 512, False)
+        d = _errs(out[:, :, :heads].cpu(), r_out, lse[:, :heads].cpu(), r_lse)
+        d.update(sample=f"{heads} of {self.h_q} heads over all {L} tokens, oracle.decode.decode_ref",
+                 ok=bool(d["out_max_abs"] <= d["out_bound"] and d["lse_max_abs"] <= 1e-4))
+        return d
+
+    def cpu_sample(self, L: int = 1 << 16, heads: int = 16):
+        from oracle import decode
+        torch.manual_seed(6)
+        kv = torch.randn((L // 64, 64, 1, 576), dtype=torch.bfloat16)
+        q = torch.randn((1, 1, heads, 576), dtype=torch.bfloat16)
+        lens, bt = torch.tensor([L], dtype=torch.int32), torch.arange(L // 64, dtype=torch.int32).view(1, -1)
+
+        def run():
+            return decode.decode_ref(lens, bt, q, kv, 512, False)
+        return run, int(L * 1152), f"{L} of {self.seqlen} tokens, {heads} of {self.h_q} heads, oracle.decode.decode_ref"
 
 
-WORKLOADS = {
-    "dense_fwd": lambda: DenseFwd(),
-    "dense_decode": lambda: DenseDecode(1),
-    "dense_decode_sq2": lambda: DenseDecode(2),
-    "sparse_decode": lambda: SparseDecode(),
-    "sparse_prefill": lambda: SparsePrefill(),
-    "dense_fwd_bwd": lambda: DenseFwdBwd(),
-}
+def make_workload(key: str, small: bool = False) -> Workload:
+    return {
+        "dense_decode": lambda: DenseDecode(1, small=small),
+        "dense_decode_sq2": lambda: DenseDecode(2, small=small),
+        "sparse_decode": lambda: SparseDecode(small=small),
+        "sparse_prefill": lambda: SparsePrefill(small=small),
+        "dense_fwd": lambda: DenseFwd(small=small),
+        "dense_fwd_bwd": lambda: DenseFwdBwd(small=small),
+        "kv_sharded_decode": lambda: KVShardedDecode(small=small),
+    }[key]()
+
+
+WORKLOADS = ["dense_decode", "dense_decode_sq2", "sparse_decode", "sparse_prefill", "dense_fwd", "dense_fwd_bwd", "kv_sharded_decode"]
 
 
 # ---------------------------------------------------------------------------------------------
@@ -427,23 +769,24 @@ def time_cpu(run, steps, warmup):
     return statistics.median(ts)
 
 
+def unit_scale(wl):
+    return 1e9 if wl.unit == "GB/s" else 1e12
+
+
 def run_reference(args, wl):
     rank, world, _ = dist_env()
     if rank != 0:
         return
-    if not hasattr(wl, "cpu_sample"):
-        print(json.dumps({"impl": "reference", "unavailable": "no CPU sample is defined for this workload; the default workload has one"}))
-        return
     wl.make_host(args.seed)
     use_all_host_threads()
-    run, nbytes, sample = wl.cpu_sample()
+    run, units, sample = wl.cpu_sample()
     steps = max(1, min(args.steps, 5))
     warm = max(1, min(args.warmup, 1))
     sec = time_cpu(run, steps, warm)
-    val = nbytes / sec / 1e9
+    val = units / sec / unit_scale(wl)
     cores = torch.get_num_threads()
     line = {"impl": "reference", "metric": wl.metric, "value": val, "unit": wl.unit, "n_gpus": args.gpus, "steps": steps,
-            "warmup": warm, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "warmup": warm, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": {"workload": wl.name, "sample": sample},
             "cpu_baseline": {"value": val, "unit": wl.unit, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -451,18 +794,193 @@ def run_reference(args, wl):
     print(json.dumps(line))
 
 
+class Runner:
+    """Times one workload on this rank; every rank runs the same sequence of collectives."""
+
+    def __init__(self, device, local, rank, world, seed):
+        self.device, self.local, self.rank, self.world, self.seed = device, local, rank, world, seed
+        self.stream = torch.cuda.current_stream()
+        if world > 1:
+            import torch.distributed as dist
+            self.dist = dist
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def allmax(self, x: float) -> float:
+        t = torch.tensor([x], dtype=torch.float64, device=self.device)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def allsum(self, x: float) -> float:
+        t = torch.tensor([x], dtype=torch.float64, device=self.device)
+        if self.world > 1:
+            self.dist.all_reduce(t)
+        return float(t.item())
+
+    def all_ok(self, ok: bool) -> bool:
+        return self.allmax(0.0 if ok else 1.0) == 0.0
+
+    def timed(self, fn, steps, per_kernel=False):
+        """Returns (ms per step as the max over ranks, [kernel ms], clocks)."""
+        pairs = None
+        if per_kernel:
+            pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+            for a, b in pairs:            # create the handles
+                a.record(self.stream)
+                b.record(self.stream)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        sampler = ClockSampler(self.local).start()
+        e0.record(self.stream)
+        for i in range(steps):
+            fn(pairs[i]) if per_kernel else fn(None)
+        e1.record(self.stream)
+        self.barrier()
+        clocks = sampler.stop()
+        ms = self.allmax(e0.elapsed_time(e1)) / steps
+        kern = [a.elapsed_time(b) for a, b in pairs] if per_kernel else []
+        return ms, kern, clocks
+
+    def e2e(self, wl, steps, run_kernel=True):
+        wl.e2e_begin()
+        for _ in range(min(3, steps)):
+            wl.step_e2e(run_kernel)
+        wl.e2e_end()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        e0.record(self.stream)
+        wl.e2e_begin()
+        for _ in range(steps):
+            wl.step_e2e(run_kernel)
+        wl.e2e_end()
+        e1.record(self.stream)
+        self.barrier()
+        return self.allmax(e0.elapsed_time(e1)) / steps
+
+    def measure(self, wl, steps, warmup, headline: bool, do_cpu: bool):
+        """Set-up, warm-up, K timed steps, roofline, parity sample, end-to-end loop.  Returns a dict (rank 0 uses it)."""
+        peaks = measured_peaks()
+        r = {"name": wl.key, "workload": wl.name, "metric": wl.metric, "unit": wl.unit, "dtype": wl.dtype, "scaling": wl.scaling,
+             "steps": steps, "warmup": warmup}
+        ok = True
+        try:
+            wl.setup(self.device, self.seed, self.rank, self.world)
+            for _ in range(warmup):
+                wl.step()
+            torch.cuda.synchronize()
+        except Exception as e:      # noqa: BLE001
+            ok = False
+            r["error"] = f"setup: {type(e).__name__}: {e}"
+            traceback.print_exc(file=sys.stderr)
+        if not self.all_ok(ok):
+            r.setdefault("error", "set-up failed on another rank")
+            return r
+        per_kernel = wl.bound == "hbm" and wl.key.startswith("dense_decode")
+        ms, kern, clocks = self.timed(lambda ev: wl.step(ev) if per_kernel else wl.step(), steps, per_kernel)
+        nbytes, nflops = self.allsum(float(wl.alg_bytes())), self.allsum(float(wl.alg_flops()))
+        gbs, tflops = nbytes / (ms * 1e-3) / 1e9, nflops / (ms * 1e-3) / 1e12
+        r.update(value=gbs if wl.unit == "GB/s" else tflops, ms_per_step=ms, gb_per_s=gbs, tflops=tflops, clocks=clocks,
+                 gpu_launches=wl.launches_per_step * steps)
+        if wl.imbalance() is not None:
+            r["imbalance_max_over_mean"] = wl.imbalance()
+        # roofline of the dominant kernel: this rank's algorithmic work / this rank's kernel time
+        if wl.bound == "hbm":
+            k_ms = statistics.mean(kern) if kern else ms
+            ach = wl.alg_bytes() / (k_ms * 1e-3) / 1e9
+            r["roofline"] = {"bound": "hbm", "kernel": wl.kernel_name, "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": ach / peaks["hbm_gbs"], "peak_source": peaks["source"], "kernel_ms": k_ms,
+                             "kernel_timed": "CUDA events around the attention kernel, recorded by the library" if kern else "whole step",
+                             "algorithmic_bytes_per_launch": wl.alg_bytes(), "traffic": wl.traffic(),
+                             "tensor_tflops": wl.alg_flops() / (k_ms * 1e-3) / 1e12,
+                             "tensor_frac_of_burst": wl.alg_flops() / (k_ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
+        else:   # whole step timed (these workloads launch their kernels back to back with nothing else)
+            ach = wl.alg_flops() / (ms * 1e-3) / 1e12
+            long_step = ms * steps > 500.0          # a stretch of seconds runs under the power cap: sustained peak
+            peak = peaks["bf16_tflops_sustained"] if long_step else peaks["bf16_tflops"]
+            r["roofline"] = {"bound": "tensor", "kernel": wl.kernel_name, "achieved": ach, "peak": peak, "unit": "TFLOP/s",
+                             "frac": ach / peak, "frac_of_burst": ach / peaks["bf16_tflops"], "peak_source": peaks["source"],
+                             "peak_kind": "sustained" if long_step else "burst", "kernel_ms": ms,
+                             "algorithmic_flops_per_launch": wl.alg_flops(), "traffic": wl.traffic()}
+        # parity of a sample of the outputs the timed path produces
+        try:
+            par = wl.parity()
+        except Exception as e:      # noqa: BLE001
+            par = {"ok": False, "error": f"{type(e).__name__}: {e}"}
+            traceback.print_exc(file=sys.stderr)
+        par["ok"] = self.all_ok(bool(par.get("ok")))
+        r["parity_checked"] = par
+        if isinstance(wl, KVShardedDecode) and self.world > 1:
+            ms_n, _, _ = self.timed(lambda ev: wl.step_nccl(), steps)
+            r["nccl_all_gather_baseline_ms"] = ms_n
+            r["peer_merge_ms"] = ms
+        # sustained: the same step for at least a second
+        if headline:
+            t0 = time.perf_counter()
+            n, tot = 0, 0.0
+            sampler = ClockSampler(self.local).start()
+            while tot < 1000.0 and time.perf_counter() - t0 < 20.0:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                self.barrier()
+                e0.record(self.stream)
+                for _ in range(steps * 5):
+                    wl.step()
+                e1.record(self.stream)
+                self.barrier()
+                tot += self.allmax(e0.elapsed_time(e1))
+                n += steps * 5
+            c = sampler.stop()
+            r["sustained"] = {"value": (nbytes if wl.unit == "GB/s" else nflops) / (tot / n * 1e-3) / unit_scale(wl), "unit": wl.unit,
+                              "steps": n, "seconds": tot / 1e3, "ms_per_step": tot / n, "clocks": c}
+        # end to end through the public API with host buffers
+        try:
+            e_steps = max(1, min(steps, wl.e2e_max_steps))
+            e_ms = self.e2e(wl, e_steps)
+            h2d, d2h = wl.e2e_bytes()
+            units = nbytes if wl.unit == "GB/s" else nflops
+            r["e2e"] = {"value": units / (e_ms * 1e-3) / unit_scale(wl), "unit": wl.unit, "ms_per_step": e_ms, "steps": e_steps,
+                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "note": "every step copies its inputs from pinned host memory and reads its results back; "
+                                + ("copies and kernels of neighbouring steps overlap (3 streams, 2 buffer sets); " if wl.e2e_buffers > 1 else "")
+                                + "the KV cache / kv tensor is resident device state"}
+            if headline:
+                c_ms = self.e2e(wl, e_steps, run_kernel=False)
+                r["e2e"]["copy_only"] = {"ms_per_step": c_ms, "fraction_of_copy_only": c_ms / e_ms,
+                                         "note": "the same copies without the kernel: what the host fabric alone allows at this N"}
+        except Exception as e:      # noqa: BLE001
+            r["e2e"] = None
+            r["e2e_error"] = f"{type(e).__name__}: {e}"
+            traceback.print_exc(file=sys.stderr)
+        if do_cpu and self.rank == 0:
+            try:
+                use_all_host_threads()
+                run, units, sample = wl.cpu_sample()
+                sec = time_cpu(run, 3 if headline else 1, 1)
+                r["cpu_baseline"] = {"value": units / sec / unit_scale(wl), "unit": wl.unit, "cores": torch.get_num_threads(), "kind": "port",
+                                     "sample": sample, "seconds": sec}
+            except Exception as e:      # noqa: BLE001
+                r["cpu_baseline"] = None
+                r["cpu_baseline_error"] = f"{type(e).__name__}: {e}"
+        return r
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dense_decode", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="dense_decode", choices=WORKLOADS)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--small", action="store_true", help="shrink the workload (profiler captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="do not run the other workloads after the default one")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    wl = WORKLOADS[args.workload]()
+    wl = make_workload(args.workload, args.small)
 
     if args.impl == "reference":
         run_reference(args, wl)
@@ -473,107 +991,46 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path (use --impl reference for the CPU baseline)")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    use_dist = world > 1
-    if use_dist:
+    if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
 
-    wl.setup(device, args.seed + rank)
-    stream = torch.cuda.current_stream()
+    runner = Runner(device, local, rank, world, args.seed)
+    head = runner.measure(wl, args.steps, args.warmup, headline=True, do_cpu=not args.no_cpu_baseline and world == 1)
+    wl.release()
 
-    def barrier():
-        if use_dist:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- device-resident timing (value) + per-kernel timing (roofline) -------------------------
-    for _ in range(args.warmup):
-        wl.step()
-    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    for a, b in pairs:            # create the handles
-        a.record(stream)
-        b.record(stream)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(local)
-    barrier()
-    sampler.start()
-    e0.record(stream)
-    for i in range(args.steps):
-        wl.step(pairs[i] if wl.bound == "hbm" else None)
-    e1.record(stream)
-    barrier()
-    clocks = sampler.stop()
-    total_ms = e0.elapsed_time(e1)
-    kern_ms = [a.elapsed_time(b) for a, b in pairs] if wl.bound == "hbm" else []
-    t = torch.tensor([total_ms], dtype=torch.float64, device=device)
-    if use_dist:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_per_step = float(t.item()) / args.steps
-    nbytes = torch.tensor([float(wl.alg_bytes())], dtype=torch.float64, device=device)
-    nflops = torch.tensor([float(wl.alg_flops())], dtype=torch.float64, device=device)
-    if use_dist:
-        dist.all_reduce(nbytes)
-        dist.all_reduce(nflops)
-    gbs = float(nbytes.item()) / (ms_per_step * 1e-3) / 1e9
-    tflops = float(nflops.item()) / (ms_per_step * 1e-3) / 1e12
-    value = gbs if wl.bound == "hbm" else tflops
-
-    # ---- end to end through the public API with host buffers -----------------------------------
-    e2e = None
-    if hasattr(wl, "step_e2e"):
-        wl.e2e_begin()
-        for _ in range(3):
-            wl.step_e2e()
-        wl.e2e_end()
-        barrier()
-        e0.record(stream)
-        wl.e2e_begin()
-        for _ in range(args.steps):
-            wl.step_e2e()
-        wl.e2e_end()
-        e1.record(stream)
-        barrier()
-        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
-        if use_dist:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item()) / args.steps
-        h2d, d2h = wl.e2e_bytes()
-        e2e = {"value": float(nbytes.item()) / (e2e_ms * 1e-3) / 1e9, "unit": wl.unit, "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "note": "every step copies q, block_table, cache_seqlens from pinned host memory and reads out, lse back; copies and kernels of neighbouring steps overlap (3 streams, 2 buffer sets); the KV cache is resident device state"}
+    extras = []
+    if args.workload == "dense_decode" and not args.no_extras and not args.small and "error" not in head:
+        for key in WORKLOADS:
+            if key == "dense_decode":
+                continue
+            w = make_workload(key)
+            steps = 20
+            r = runner.measure(w, steps, 3, headline=False, do_cpu=not args.no_cpu_baseline and world == 1)
+            w.release()
+            extras.append(r)
 
     if rank == 0:
-        peaks = measured_peaks()
-        if wl.bound == "hbm":
-            k_ms = statistics.mean(kern_ms)
-            achieved = wl.alg_bytes() / (k_ms * 1e-3) / 1e9
-            roof = {"bound": "hbm", "kernel": wl.kernel_name, "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "kernel_ms": k_ms,
-                    "algorithmic_bytes_per_launch": wl.alg_bytes(), "traffic": TRAFFIC_BYTES.get(args.workload),
-                    "tensor_tflops": wl.alg_flops() / (k_ms * 1e-3) / 1e12,
-                    "tensor_frac_of_burst": wl.alg_flops() / (k_ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
-        else:   # whole step timed (these workloads launch their kernels back to back with nothing else)
-            achieved = wl.alg_flops() / (ms_per_step * 1e-3) / 1e12
-            roof = {"bound": "tensor", "kernel": wl.kernel_name, "achieved": achieved, "peak": peaks["bf16_tflops"],
-                    "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "peak_source": peaks["source"],
-                    "kernel_ms": ms_per_step, "algorithmic_flops_per_launch": wl.alg_flops(), "traffic": None}
-        cpu = None
-        if not args.no_cpu_baseline and hasattr(wl, "cpu_sample"):
-            use_all_host_threads()
-            run, cbytes, sample = wl.cpu_sample()
-            sec = time_cpu(run, 3, 1)
-            cpu = {"value": cbytes / sec / 1e9, "unit": wl.unit, "cores": torch.get_num_threads(), "kind": "port",
-                   "sample": sample, "seconds": sec}
-        line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-                "config": {"workload": wl.name, "global_batch": wl.b * world, "parallelism": f"requests sharded x{world}, no collective",
-                           "l2": "inputs (>=600 MB per GPU) larger than the 126 MB L2; no flush"},
-                "tflops": tflops, "roofline": roof, "cpu_baseline": cpu,
-                "e2e": e2e, "gb_per_s": gbs,
-                "gpu_launches": wl.launches_per_step * args.steps, "clocks": clocks}
-        print(json.dumps(line))
-    if use_dist:
+        if "error" in head:
+            print(json.dumps({"metric": wl.metric, "error": head["error"]}))
+        else:
+            line = {"metric": wl.metric, "value": head["value"], "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+                    "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": wl.scaling,
+                    "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+                    "config": {"workload": wl.name, "global_batch": wl.b * world if wl.scaling == "weak" else wl.b,
+                               "parallelism": f"{wl.sharding} x{world}",
+                               "l2": "inputs (>=600 MB per GPU) larger than the 126 MB L2; no flush"},
+                    "tflops": head["tflops"], "gb_per_s": head["gb_per_s"], "roofline": head["roofline"],
+                    "cpu_baseline": head.get("cpu_baseline"), "e2e": head.get("e2e"), "parity_checked": head.get("parity_checked"),
+                    "sustained": head.get("sustained"), "gpu_launches": head["gpu_launches"], "clocks": head["clocks"]}
+            for k in ("imbalance_max_over_mean", "nccl_all_gather_baseline_ms", "peer_merge_ms", "e2e_error"):
+                if k in head:
+                    line[k] = head[k]
+            if extras:
+                line["workloads"] = extras
+            print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
         dist.destroy_process_group()
 
 

@@ -58,6 +58,48 @@ int device_info(int device, DevInfo* out) {
   return FMLA_OK;
 }
 
+// ---- device-side timeouts, visible to the host without a synchronise ----------------------------------
+// A bounded wait that expires inside a kernel records a code in a device status word AND stores it into a
+// word of this page of host memory, which is registered (page-locked, mapped) once per process and whose
+// device-side address every kernel translation unit learns once per device.  The next library call on that
+// device reads the word with a plain load and refuses to launch on top of a failed pipeline.
+constexpr int kStatusStride = 16;                       // ints: one 64-byte line per device
+alignas(4096) int g_host_status[64 * kStatusStride];
+std::mutex g_status_mutex;
+bool g_status_registered = false, g_status_unavailable = false;
+bool g_mirror_set[64] = {};
+
+void ensure_status_mirror(int dev) {
+  if (g_mirror_set[dev] || g_status_unavailable) return;
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  if (g_mirror_set[dev] || g_status_unavailable) return;
+  if (!g_status_registered) {
+    if (cudaHostRegister(g_host_status, sizeof(g_host_status), cudaHostRegisterMapped | cudaHostRegisterPortable) != cudaSuccess) {
+      (void)cudaGetLastError();
+      g_status_unavailable = true;      // the device status words and fmla_device_status() still work
+      return;
+    }
+    g_status_registered = true;
+  }
+  void* dptr = nullptr;
+  if (cudaHostGetDevicePointer(&dptr, &g_host_status[dev * kStatusStride], 0) != cudaSuccess) {
+    (void)cudaGetLastError();
+    g_status_unavailable = true;
+    return;
+  }
+  int* w = static_cast<int*>(dptr);
+  if (fmla::set_status_mirror_mla(w) != cudaSuccess || fmla::set_status_mirror_pair(w) != cudaSuccess ||
+      fmla::set_status_mirror_merge(w) != cudaSuccess ||
+      fmla::set_status_mirror_dense_fwd(w) != cudaSuccess || fmla::set_status_mirror_dense_bwd(w) != cudaSuccess) {
+    (void)cudaGetLastError();
+    g_status_unavailable = true;
+    return;
+  }
+  g_mirror_set[dev] = true;
+}
+
+// Common prologue of every launching entry point: right architecture, status mirror in place, and no
+// failure left behind by an earlier launch on this device.
 int require_blackwell() {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -66,6 +108,12 @@ int require_blackwell() {
   int rc = device_info(dev, &di);
   if (rc) return rc;
   if (di.major != 10) return fail(FMLA_ERR_WRONG_ARCH, "device %d is sm_%d%d; this library is built for sm_100a only", dev, di.major, di.minor);
+  ensure_status_mirror(dev);
+  const int code = *reinterpret_cast<volatile int*>(&g_host_status[dev * kStatusStride]);
+  if (code != 0)
+    return fail(FMLA_ERR_DEVICE_TIMEOUT,
+                "an earlier launch on device %d gave up on a bounded device-side wait (code %d): its outputs are not valid; "
+                "call fmla_device_status(&status, 1) to clear the condition", dev, code);
   return FMLA_OK;
 }
 
@@ -171,6 +219,7 @@ static int decode_impl(const fmla_decode_params* P, const fmla_peer_push* push, 
     FMLA_REQUIRE(a.block_table != nullptr, "block_table is null");
     FMLA_REQUIRE(a.k_stride_block % 8 == 0 && a.k_stride_row % 8 == 0 && a.k_stride_head % 8 == 0, "kcache strides must be multiples of 8 elements");
   }
+  FMLA_REQUIRE(!(push && sparse), "the peer push is implemented for the dense decode");
   int rc = require_blackwell();
   if (rc) return rc;
 
@@ -209,7 +258,6 @@ static int decode_impl(const fmla_decode_params* P, const fmla_peer_push* push, 
     if (e != cudaSuccess) return cuda_fail(e, "cudaEventRecord");
   }
   if (push) {
-    FMLA_REQUIRE(!sparse, "the peer push is implemented for the dense decode");
     e = fmla::launch_decode_combine_push(k, s);
   } else {
     e = fmla::launch_decode_combine(k, s);
@@ -236,6 +284,7 @@ int fmla_merge_peer_partials(const float* part_lse, const float* part_o, int num
   FMLA_REQUIRE(d_v == 512, "Only head_size_v == 512 is supported");
   FMLA_REQUIRE(max_polls > 0, "max_polls must be positive");
   FMLA_REQUIRE(aligned16(part_o) && aligned16(out) && o_stride_row % 8 == 0, "part_o/out must be 16-byte aligned, stride a multiple of 8");
+  if (int rc = require_blackwell()) return rc;
   cudaError_t e = fmla::launch_merge_peer_partials(part_lse, part_o, num_parts, rows, out, o_stride_row, lse, flags, epoch, max_polls,
                                                   static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? FMLA_OK : cuda_fail(e, "peer merge launch");
@@ -248,6 +297,7 @@ int fmla_combine_partials(const float* lse_accum, const float* o_accum, int num_
   FMLA_REQUIRE(d_v == 512, "Only head_size_v == 512 is supported");
   FMLA_REQUIRE(num_parts <= 4096, "num_parts too large");
   FMLA_REQUIRE(aligned16(o_accum) && aligned16(out) && o_stride_row % 8 == 0, "o_accum/out must be 16-byte aligned, stride a multiple of 8");
+  if (int rc = require_blackwell()) return rc;
   cudaError_t e = fmla::launch_combine_partials(lse_accum, o_accum, num_parts, rows, out, o_stride_row, lse,
                                                static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? FMLA_OK : cuda_fail(e, "combine launch");
@@ -350,6 +400,10 @@ int fmla_device_status(int* status_host, int reset) {
   FMLA_REQUIRE(status_host != nullptr, "status_host is null");
   cudaError_t e = fmla::read_decode_tc_status(status_host, reset != 0);
   if (e != cudaSuccess) return cuda_fail(e, "reading the device status word");
+  int pair_status = 0;
+  e = fmla::read_decode_pair_status(&pair_status, reset != 0);
+  if (e != cudaSuccess) return cuda_fail(e, "reading the device status word");
+  if (*status_host == 0) *status_host = pair_status;
   int merge_status = 0;
   e = fmla::read_merge_status(&merge_status, reset != 0);
   if (e != cudaSuccess) return cuda_fail(e, "reading the device status word");
@@ -361,6 +415,12 @@ int fmla_device_status(int* status_host, int reset) {
   e = fmla::read_dense_bwd_tc_status(&dense_status, reset != 0);
   if (e != cudaSuccess) return cuda_fail(e, "reading the device status word");
   if (*status_host == 0) *status_host = dense_status;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+    volatile int* w = reinterpret_cast<volatile int*>(&g_host_status[dev * kStatusStride]);
+    if (*status_host == 0) *status_host = *w;
+    if (reset) *w = 0;
+  }
   return *status_host == 0 ? FMLA_OK : fail(FMLA_ERR_DEVICE_TIMEOUT, "a bounded device-side wait expired (code %d)", *status_host);
 }
 

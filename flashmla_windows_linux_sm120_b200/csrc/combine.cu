@@ -10,13 +10,16 @@
 // contiguous per load instruction.
 #include "fmla_common.cuh"
 #include "kernels.h"
+#include "tc_common.cuh"
 
 namespace fmla {
 
 constexpr int kCombineWarps = 8;
 
-// lse_part(i) / o_part(i) address part i of this row.
-template <class LseAt, class OAt>
+// lse_part(i) / o_part(i) address part i of this row.  COHERENT: the partial outputs may have been written by
+// another GPU while this kernel was already resident (peer merge), so they are read with ld.global.cv
+// instead of the non-coherent path, which is undefined for memory modified during the kernel's lifetime.
+template <bool COHERENT = false, class LseAt, class OAt>
 __device__ __forceinline__ void combine_row(int nparts, LseAt lse_at, OAt o_at, float* s_w, __nv_bfloat16* out_row,
                                             float* lse_out, bool f16 = false) {
   const int lane = threadIdx.x & 31;
@@ -43,7 +46,7 @@ __device__ __forceinline__ void combine_row(int nparts, LseAt lse_at, OAt o_at, 
     const float4* src = reinterpret_cast<const float4*>(o_at(i));
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float4 v = __ldg(src + j * 32 + lane);
+      const float4 v = COHERENT ? __ldcv(src + j * 32 + lane) : __ldg(src + j * 32 + lane);
       acc[j].x += w * v.x;
       acc[j].y += w * v.y;
       acc[j].z += w * v.z;
@@ -187,7 +190,7 @@ merge_peer_partials_kernel(const float* __restrict__ lse_accum, const float* __r
         __nanosleep(200);
       }
     }
-    if (!ok) atomicCAS(status, 0, 20);
+    if (!ok) tc::report_status(status, 20);
     s_ok = ok;
   }
   __syncthreads();
@@ -195,7 +198,7 @@ merge_peer_partials_kernel(const float* __restrict__ lse_accum, const float* __r
   const int warp = threadIdx.x >> 5;
   const int r = blockIdx.x * kCombineWarps + warp;
   if (r >= rows) return;
-  combine_row(
+  combine_row<true>(
       nparts, [&](int i) { return __ldcv(lse_accum + (int64_t)i * rows + r); },
       [&](int i) { return o_accum + ((int64_t)i * rows + r) * 512; }, s_weights + warp * nparts, out + r * o_stride_row,
       lse + r);
@@ -203,10 +206,21 @@ merge_peer_partials_kernel(const float* __restrict__ lse_accum, const float* __r
 
 __device__ int g_merge_status = 0;
 
+cudaError_t set_status_mirror_merge(int* mapped_host_word) { return tc::set_status_mirror(mapped_host_word); }
+
+// The merge kernels keep one weight per (warp, part) in dynamic shared memory; above 48 KB the limit of the
+// kernel has to be raised first.
+template <class Kernel>
+static cudaError_t allow_dynamic_smem(Kernel kernel, size_t bytes) {
+  if (bytes <= 48 * 1024) return cudaSuccess;
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+}
+
 cudaError_t launch_decode_combine_push(const DecodeKernelParams& p, cudaStream_t stream) {
   const int rows = p.h_k * p.s_q * p.hq_per_hk;
   dim3 grid(p.b, (rows + kCombineWarps - 1) / kCombineWarps);
   const size_t smem = sizeof(float) * kCombineWarps * p.num_sm_parts;
+  if (cudaError_t e = allow_dynamic_smem(decode_combine_push_kernel, smem); e != cudaSuccess) return e;
   decode_combine_push_kernel<<<grid, kCombineWarps * 32, smem, stream>>>(p);
   return cudaGetLastError();
 }
@@ -218,6 +232,8 @@ cudaError_t launch_merge_peer_partials(const float* lse_accum, const float* o_ac
   cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_merge_status);
   if (e != cudaSuccess) return e;
   const size_t smem = sizeof(float) * kCombineWarps * num_parts;
+  e = allow_dynamic_smem(merge_peer_partials_kernel, smem);
+  if (e != cudaSuccess) return e;
   merge_peer_partials_kernel<<<(rows + kCombineWarps - 1) / kCombineWarps, kCombineWarps * 32, smem, stream>>>(
       lse_accum, o_accum, num_parts, rows, reinterpret_cast<__nv_bfloat16*>(out), o_stride_row, lse, flags, epoch, max_polls,
       status);
@@ -238,6 +254,7 @@ cudaError_t launch_decode_combine(const DecodeKernelParams& p, cudaStream_t stre
   const int rows = p.h_k * p.s_q * p.hq_per_hk;
   dim3 grid(p.b, (rows + kCombineWarps - 1) / kCombineWarps);
   const size_t smem = sizeof(float) * kCombineWarps * p.num_sm_parts;
+  if (cudaError_t e = allow_dynamic_smem(decode_combine_kernel, smem); e != cudaSuccess) return e;
   decode_combine_kernel<<<grid, kCombineWarps * 32, smem, stream>>>(p);
   return cudaGetLastError();
 }
@@ -245,6 +262,7 @@ cudaError_t launch_decode_combine(const DecodeKernelParams& p, cudaStream_t stre
 cudaError_t launch_combine_partials(const float* lse_accum, const float* o_accum, int num_parts, int rows, void* out,
                                     int64_t o_stride_row, float* lse, cudaStream_t stream) {
   const size_t smem = sizeof(float) * kCombineWarps * num_parts;
+  if (cudaError_t e = allow_dynamic_smem(combine_partials_kernel, smem); e != cudaSuccess) return e;
   combine_partials_kernel<<<(rows + kCombineWarps - 1) / kCombineWarps, kCombineWarps * 32, smem, stream>>>(
       lse_accum, o_accum, num_parts, rows, reinterpret_cast<__nv_bfloat16*>(out), o_stride_row, lse);
   return cudaGetLastError();

@@ -149,7 +149,7 @@ dense_bwd_dq_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid
   const int m_base = (gridDim.x - 1 - blockIdx.x) * 128;    // the tiles with the most keys first
   if (m_base >= lq) return;
   if ((sbase & 1023u) != 0) {
-    if (tid == 0) atomicCAS(status, 0, 30);
+    if (tid == 0) tc::report_status(status, 30);
     return;
   }
   int nblk = (lk + 63) >> 6;
@@ -366,7 +366,7 @@ dense_bwd_dkdv_tc_kernel(const __grid_constant__ DenseKernelParams p, const __gr
   const int n_base = blockIdx.x * 128;                       // with a causal mask the first key tiles see the most queries
   if (n_base >= lk) return;
   if ((sbase & 1023u) != 0) {
-    if (tid == 0) atomicCAS(status, 0, 30);
+    if (tid == 0) tc::report_status(status, 30);
     return;
   }
   // query blocks [jb_lo, jb_hi) of 64 rows that see at least one key of this tile
@@ -607,6 +607,8 @@ extern "C" int fmla_debug_read_dense_bwd_trace(long long* host, int n) {
   return (int)cudaMemcpyFromSymbol(host, g_dense_bwd_trace, sizeof(long long) * n);
 }
 #endif
+
+cudaError_t set_status_mirror_dense_bwd(int* mapped_host_word) { return tc::set_status_mirror(mapped_host_word); }
 
 cudaError_t read_dense_bwd_tc_status(int* host_status, bool reset) {
   cudaError_t e = cudaMemcpyFromSymbol(host_status, g_dense_bwd_tc_status, sizeof(int));

@@ -97,7 +97,7 @@ dense_fwd_tc_kernel(const __grid_constant__ DenseKernelParams p, const __grid_co
   const int m_base = (gridDim.x - 1 - blockIdx.x) * 256;
   if (m_base >= lq) return;
   if ((sbase & 1023u) != 0) {   // the swizzled tiles need a 1024-byte aligned base
-    if (tid == 0) atomicCAS(status, 0, 30);
+    if (tid == 0) tc::report_status(status, 30);
     return;
   }
   // both tiles walk the key blocks the last row of the CTA needs; blocks a row cannot see are masked
@@ -371,6 +371,8 @@ cudaError_t launch_dense_fwd_tc(const DenseKernelParams& p, cudaStream_t stream)
   if (p.d_qk == 192) return launch_fwd_tc<192>(p, tq, tk, tv, stream);
   return launch_fwd_tc<128>(p, tq, tk, tv, stream);
 }
+
+cudaError_t set_status_mirror_dense_fwd(int* mapped_host_word) { return tc::set_status_mirror(mapped_host_word); }
 
 cudaError_t read_dense_tc_status(int* host_status, bool reset) {
   cudaError_t e = cudaMemcpyFromSymbol(host_status, g_dense_tc_status, sizeof(int));

@@ -81,6 +81,14 @@ struct DenseKernelParams {
 // records `message` as the calling thread's last error and returns `code`
 int set_error(int code, const char* message);
 
+// Each kernel translation unit keeps a pointer to a host-mapped status word beside its device status word
+// (tc_common.cuh); these set it for the current device.
+cudaError_t set_status_mirror_mla(int* mapped_host_word);
+cudaError_t set_status_mirror_pair(int* mapped_host_word);
+cudaError_t set_status_mirror_merge(int* mapped_host_word);
+cudaError_t set_status_mirror_dense_fwd(int* mapped_host_word);
+cudaError_t set_status_mirror_dense_bwd(int* mapped_host_word);
+
 cudaError_t launch_get_mla_metadata(const int* seqlens_k, int batch, int num_sm_parts, int topk, int* md,
                                     int* num_splits, cudaStream_t stream);
 // tcgen05 / TMA / TMEM kernels (mla_tc.cu): dense decode, sparse FP8 decode, sparse prefill
@@ -89,6 +97,11 @@ cudaError_t launch_decode_sparse_tc(const DecodeKernelParams& p, cudaStream_t st
 cudaError_t launch_sparse_prefill_tc(const SparsePrefillKernelParams& p, cudaStream_t stream);
 // reads (and optionally clears) the status word the tcgen05 kernels set when a bounded wait expires
 cudaError_t read_decode_tc_status(int* host_status, bool reset);
+// dense decode as a CTA pair (mla_pair.cu): 128 heads per pair, tcgen05 cta_group::2; used by
+// launch_decode_dense_tc whenever the heads per kv head are a multiple of 128
+bool decode_dense_pair_applies(const DecodeKernelParams& p);
+cudaError_t launch_decode_dense_pair(const DecodeKernelParams& p, cudaStream_t stream);
+cudaError_t read_decode_pair_status(int* host_status, bool reset);
 // Merge of split partials for a decode call (reads num_splits; skips unsplit requests).
 cudaError_t launch_decode_combine(const DecodeKernelParams& p, cudaStream_t stream);
 // Stand-alone merge of num_parts partial slots for `rows` rows.

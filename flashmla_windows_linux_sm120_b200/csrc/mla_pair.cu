@@ -1,0 +1,560 @@
+// Dense BF16 / FP16 split-KV MLA decode for sm_100a as a CTA pair (cluster of two CTAs, tcgen05 cta_group::2).
+//
+// The pair owns 128 query heads of one (query token, kv head, partition): CTA r of the pair (cluster rank r)
+// owns heads 64r .. 64r+63, i.e. the Q tile, the S tile, the P tile and the O accumulator of those heads.
+// One thread of the leader (rank 0) issues every MMA for both SMs:
+//   S = Q K^T   36 x tcgen05.mma.cta_group::2 m128n64k16: the B operand (64 tokens x 576) is split along N, so
+//               each CTA stages only ITS 32 token rows of a page (36 KB) -- the pair reads a page for S once
+//   O += P V    8 x tcgen05.mma.cta_group::2 m128n256k16: B = V, split along N = value columns, so each CTA
+//               stages 64 tokens x 256 value columns (32 KB): chunks {2r, 2r+1, 4+2r, 5+2r} of the page
+// What this buys over one CTA per 64 heads with a 72 KB page stage that is held from its load until the end
+// of its P V: the K part is released right after S and the V part is loaded independently of it, so two
+// small rings (2 x 36 KB + 2 x 32 KB) keep more loads in flight per SM than two 72 KB stages, and the paired
+// instructions run at 25 / 65 clocks (S / P V) instead of 32 / 81.
+//
+//   warps 0-3 softmax : as in mla_tc.cu (TMEM lane = row + 64 * (token >= 32)); arrivals that the issuing
+//                       thread waits for go to the leader's barriers (remote arrive from rank 1)
+//   warp 4   K loader : Q tile, then per 64-token block the CTA's 32 token rows; the copies complete on the
+//                       LEADER's barrier (cp.async.bulk.tensor ... cta_group::2, no multicast)
+//   warp 5   MMA      : rank 0 only
+//   warp 6   V loader : per block 4 boxes of 64 rows x 64 columns, completing on a local barrier
+//   warp 7   V relay  : waits for the local V part, clears the rows of the last page that lie beyond the
+//                       sequence (they may hold NaN and 0 * NaN must not reach O), tells the leader
+// TMEM (512 columns per CTA, allocated as a pair): O = [0,256), S[0] = [256,288), S[1] = [288,320); layouts as
+// in mla_tc.cu (the 64-row halves of an M=128 pair instruction have the layout of the M=64 .ws form).
+//
+// Semantics follow csrc/sm90/decode/dense/splitkv_mla.cu:948-957, 1022-1042, 1237-1269 of the reference
+// (borders, split outputs, LSE conventions).  Every wait is bounded; on expiry the pair drains and frees
+// its tensor memory.
+#include "kernels.h"
+#include "mla_work.cuh"
+#include "tc_common.cuh"
+
+#include <cuda.h>
+
+namespace fmla {
+
+namespace ptc {
+constexpr int kChunkBytes = 64 * 128;             // Q / P / V chunk: [64 rows x 64 x 16-bit], 128-byte rows
+constexpr int kQBytes = 9 * kChunkBytes;          // 64 heads x 576
+constexpr int kKChunkBytes = 32 * 128;            // K chunk of this CTA: [32 token rows x 64 columns]
+constexpr int kKStageBytes = 9 * kKChunkBytes;    // 36 864
+constexpr int kVStageBytes = 4 * kChunkBytes;     // 32 768: 64 tokens x 256 value columns
+constexpr int Q_OFF = 0;
+constexpr int K_OFF = Q_OFF + kQBytes;            // 2 stages
+constexpr int V_OFF = K_OFF + 2 * kKStageBytes;   // 2 stages
+constexpr int P_OFF = V_OFF + 2 * kVStageBytes;   // [64 x 64]
+constexpr int BAR_OFF = P_OFF + kChunkBytes;
+constexpr int MX_OFF = BAR_OFF + 256;             // float [3][128] exchange
+constexpr int MISC_OFF = MX_OFF + 1536;
+constexpr int SMEM_BYTES = MISC_OFF + 64;
+// leader-side barriers (waited on by the MMA warp of rank 0; arrivals come from both CTAs)
+// and per-CTA barriers (each CTA waits on its own copy; the leader's commits arrive on both copies)
+enum Bar { Q_FULL = 0, K_FULL0, K_FULL1, V_FULL0, V_FULL1, S_EMPTY0, S_EMPTY1, P_FULL, O_EMPTY,
+           Q_EMPTY, K_EMPTY0, K_EMPTY1, V_EMPTY0, V_EMPTY1, V_LAND0, V_LAND1, S_FULL0, S_FULL1, P_EMPTY, O_FULL, NUM_BARS };
+constexpr int TMEM_O = 0, TMEM_S = 256;
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory limit per CTA");
+static_assert(NUM_BARS * 8 <= 256, "barrier area too small");
+constexpr float kRescaleThreshold = 8.0f;
+constexpr int kThreads = 256;
+}  // namespace ptc
+
+__device__ int g_decode_pair_status = 0;
+
+#ifdef FMLA_TRACE
+__device__ long long g_pair_trace[64 * 16];
+#define FMLA_PTRACE_AT(blk, slot)                                                          \
+  do {                                                                                      \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (blk) < 64) g_pair_trace[(blk) * 16 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define FMLA_PTRACE_AT(blk, slot) do {} while (0)
+#endif
+
+__device__ __forceinline__ void pst_shared_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// The 36 S instructions of one block in stage ST: descriptors are a warp-uniform base plus an immediate.
+template <int ST>
+__device__ __forceinline__ void s_block_pair(uint32_t tmem, uint64_t desc_q, uint64_t desc_k, uint32_t idesc) {
+  using namespace ptc;
+#pragma unroll
+  for (int c = 0; c < 9; ++c)
+#pragma unroll
+    for (int s = 0; s < 4; ++s)
+      tc::mma_pair_ss(tmem + TMEM_S + ST * 32, tc::desc_advance(desc_q, c * kChunkBytes + s * 32),
+                      tc::desc_advance(desc_k, ST * kKStageBytes + c * kKChunkBytes + s * 32), idesc, (c | s) ? 1u : 0u);
+}
+template <int ST>
+__device__ __forceinline__ void pv_block_pair(uint32_t tmem, uint64_t desc_p, uint64_t desc_v, uint32_t idesc, bool first) {
+  using namespace ptc;
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+#pragma unroll
+    for (int s = 0; s < 4; ++s)
+      tc::mma_pair_ss(tmem + TMEM_O + h * 128, tc::desc_advance(desc_p, s * 32),
+                      tc::desc_advance(desc_v, ST * kVStageBytes + h * 2 * kChunkBytes + s * 2048), idesc, (first && s == 0) ? 0u : 1u);
+}
+
+// grid (s_q * hq_per_hk / 64, h_k, parts), clusters of two CTAs along x; 256 threads
+template <bool F16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(ptc::kThreads, 1)
+mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtensorMap tmap_q,
+                const __grid_constant__ CUtensorMap tmap_k32, const __grid_constant__ CUtensorMap tmap_v64) {
+  using namespace ptc;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t sQ = sbase + Q_OFF, sK = sbase + K_OFF, sV = sbase + V_OFF, sP = sbase + P_OFF;
+  auto bar = [&](int i) { return sbase + BAR_OFF + i * 8; };
+  float* sMx = reinterpret_cast<float*>(smem + MX_OFF);
+  volatile uint32_t* sTmem = reinterpret_cast<volatile uint32_t*>(smem + MISC_OFF);
+  volatile int* sAbort = reinterpret_cast<volatile int*>(smem + MISC_OFF + 8);
+  int* status = &g_decode_pair_status;
+  const DecodeKernelParams& p = P.d;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = tc::cluster_rank();
+  const Tile tile = make_tile<kDense>(P);
+  if (tile.n_work == 0) return;                 // both CTAs of a pair see the same schedule row
+  const bool misaligned = (sbase & 1023u) != 0;  // the swizzled tiles need a 1024-byte aligned base
+  auto lbar = [&](int i) { return tc::mapa(bar(i), 0); };    // the leader's copy of barrier i
+  const float scale_log2 = p.scale_log2;
+
+  if (tid == 0) {
+    tc::mbar_init(bar(Q_FULL), 2);
+    tc::mbar_init(bar(K_FULL0), 2);
+    tc::mbar_init(bar(K_FULL1), 2);
+    tc::mbar_init(bar(V_FULL0), 2);
+    tc::mbar_init(bar(V_FULL1), 2);
+    tc::mbar_init(bar(S_EMPTY0), 256);
+    tc::mbar_init(bar(S_EMPTY1), 256);
+    tc::mbar_init(bar(P_FULL), 256);
+    tc::mbar_init(bar(O_EMPTY), 256);
+    for (int i = Q_EMPTY; i < NUM_BARS; ++i) tc::mbar_init(bar(i), 1);
+    tc::fence_mbar_init();
+    *sAbort = 0;
+    if (misaligned) tc::report_status(status, 30);
+  }
+  if (warp == 5) tc::tmem_alloc_pair(sbase + MISC_OFF, 512);
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::cluster_sync_all();      // barriers of both CTAs exist before anything is sent to them
+  tc::tc_fence_after();
+  const uint32_t tmem = *sTmem;
+
+  if (misaligned) {
+    // nothing was issued; fall through to the common exit
+  } else if (warp == 4) {
+    // ================================ Q and K loader ===================================
+    if (tc::elect_one()) {
+      tc::prefetch_tensormap(&tmap_q);
+      tc::prefetch_tensormap(&tmap_k32);
+      int g = 0, req = 0;
+      bool alive = true;
+      for (int wi = 0; wi < tile.n_work && alive; ++wi) {
+        const Work r = get_work<kDense>(P, tile, wi);
+        if (r.blk_hi == r.blk_lo) continue;
+        alive = tc::mbar_wait(bar(Q_EMPTY), (req & 1) ^ 1, status, 101);
+        if (!alive) break;
+        tc::mbar_arrive_expect_tx_cluster(lbar(Q_FULL), kQBytes);
+#pragma unroll
+        for (int c = 0; c < 9; ++c) tc::tma_load_4d_pair(sQ + c * kChunkBytes, &tmap_q, c * 64, tile.head0, tile.sq, r.batch, lbar(Q_FULL));
+        const int* bt = p.block_table + r.batch * p.block_table_stride_b;
+        int page_next = __ldg(bt + r.blk_lo);
+        for (int blk = r.blk_lo; blk < r.blk_hi; ++blk, ++g) {
+          const int st = g & 1;
+          const int page = page_next;
+          if (blk + 1 < r.blk_hi) page_next = __ldg(bt + blk + 1);
+          alive = tc::mbar_wait(bar(K_EMPTY0 + st), ((g >> 1) & 1) ^ 1, status, 102);
+          if (!alive) break;
+          FMLA_PTRACE_AT(g, 0);
+          tc::mbar_arrive_expect_tx_cluster(lbar(K_FULL0 + st), kKStageBytes);
+#pragma unroll
+          for (int c = 0; c < 9; ++c)
+            tc::tma_load_4d_pair(sK + st * kKStageBytes + c * kKChunkBytes, &tmap_k32, c * 64, tile.kh, 32 * static_cast<int>(rank), page, lbar(K_FULL0 + st));
+        }
+        ++req;
+      }
+    }
+  } else if (warp == 6) {
+    // ================================ V loader =========================================
+    if (tc::elect_one()) {
+      tc::prefetch_tensormap(&tmap_v64);
+      int g = 0;
+      bool alive = true;
+      for (int wi = 0; wi < tile.n_work && alive; ++wi) {
+        const Work r = get_work<kDense>(P, tile, wi);
+        const int* bt = p.block_table + r.batch * p.block_table_stride_b;
+        for (int blk = r.blk_lo; blk < r.blk_hi; ++blk, ++g) {
+          const int st = g & 1;
+          const int page = __ldg(bt + blk);
+          alive = tc::mbar_wait(bar(V_EMPTY0 + st), ((g >> 1) & 1) ^ 1, status, 103);
+          if (!alive) break;
+          tc::mbar_arrive_expect_tx(bar(V_LAND0 + st), kVStageBytes);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int chunk = (i >> 1) * 4 + 2 * static_cast<int>(rank) + (i & 1);     // value columns 64*chunk ..
+            tc::tma_load_4d(sV + st * kVStageBytes + i * kChunkBytes, &tmap_v64, chunk * 64, tile.kh, 0, page, bar(V_LAND0 + st));
+          }
+        }
+      }
+    }
+  } else if (warp == 7) {
+    // ================================ V relay ==========================================
+    int g = 0;
+    bool alive = true;
+    for (int wi = 0; wi < tile.n_work && alive; ++wi) {
+      const Work r = get_work<kDense>(P, tile, wi);
+      for (int blk = r.blk_lo; blk < r.blk_hi && alive; ++blk, ++g) {
+        const int st = g & 1;
+        alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(V_LAND0 + st), (g >> 1) & 1, status, 104));
+        if (!alive) break;
+        const int rows_valid = r.seqlen - blk * 64;
+        if (rows_valid < 64) {
+          unsigned char* stage = smem + V_OFF + st * kVStageBytes;
+          const int nrows = 64 - rows_valid;
+          for (int i = lane; i < nrows * 32; i += 32) {
+            const int row = rows_valid + (i >> 5), c16 = i & 31;            // 4 chunks x 8 pieces of 16 bytes per row
+            *reinterpret_cast<uint4*>(stage + (c16 >> 3) * kChunkBytes + row * 128 + (c16 & 7) * 16) = make_uint4(0, 0, 0, 0);
+          }
+          tc::fence_proxy_async_smem();
+          __syncwarp();
+        }
+        if (lane == 0) tc::mbar_arrive_cluster(lbar(V_FULL0 + st));
+      }
+    }
+  } else if (warp == 5) {
+    // ================================ MMA issuer (leader only) =========================
+    if (rank == 0) {
+      constexpr uint32_t idesc_s = tc::idesc_bf16_f32(128, 64, 0, 0, F16);
+      constexpr uint32_t idesc_o = tc::idesc_bf16_f32(128, 256, 0, 1, F16);
+      const uint64_t desc_q = tc::smem_desc_sw128(sQ, 16, 1024);             // A of S: K-major
+      const uint64_t desc_k = tc::smem_desc_sw128(sK, 16, 1024);             // B of S: K-major, 32 rows per CTA (stage 0)
+      const uint64_t desc_p = tc::smem_desc_sw128(sP, 16, 1024);             // A of PV: K-major
+      const uint64_t desc_v = tc::smem_desc_sw128(sV, kChunkBytes, 1024);    // B of PV: MN-major, 64-wide column groups 8 KB apart
+      // every commit goes to the barrier copy of each CTA (two plain commits, no multicast)
+      auto commit_both = [&](int b) {
+        tc::tc_commit_pair(bar(b));
+        tc::tc_commit_pair(tc::mapa(bar(b), 1));
+      };
+      int g = 0, req = 0;
+      bool alive = true;
+      for (int wi = 0; wi < tile.n_work && alive; ++wi) {
+        const Work r = get_work<kDense>(P, tile, wi);
+        const int nblk = r.blk_hi - r.blk_lo;
+        if (nblk == 0) continue;
+        alive = __all_sync(0xffffffffu, tc::mbar_wait_cluster(bar(Q_FULL), req & 1, status, 105));
+        // One poll reads every barrier of interest, one per lane:
+        //   lane 0 P_FULL(jp)  lane 1 O_EMPTY  lane 2 V_FULL(jp)  lane 3 S_EMPTY(js)  lane 4 K_FULL(js)
+        int js = 0, jp = 0, idle = 0;
+        while (jp < nblk && alive) {
+          const int gs = g + min(js, nblk - 1), sts = gs & 1;
+          const uint32_t phs = (gs >> 1) & 1;
+          const int gp = g + jp, stp = gp & 1;
+          const uint32_t php = (gp >> 1) & 1;
+          int pb = P_FULL;
+          uint32_t pp = gp & 1;
+          if (lane == 1) { pb = O_EMPTY; pp = (req & 1) ^ 1; }
+          if (lane == 2) { pb = V_FULL0 + stp; pp = php; }
+          if (lane == 3) { pb = S_EMPTY0 + sts; pp = phs ^ 1; }
+          if (lane >= 4) { pb = K_FULL0 + sts; pp = phs; }
+          const bool hit = lane < 5 && tc::mbar_test_wait_cluster(bar(pb), pp);
+          const uint32_t m = __ballot_sync(0xffffffffu, hit);
+          bool did = false;
+          if (jp < js && (m & 5u) == 5u && (jp > 0 || (m & 2u))) {
+            tc::tc_fence_after();
+            if (lane == 0) FMLA_PTRACE_AT(gp, 4);
+            if (tc::elect_one()) {
+              if (stp == 0) pv_block_pair<0>(tmem, desc_p, desc_v, idesc_o, jp == 0);
+              else pv_block_pair<1>(tmem, desc_p, desc_v, idesc_o, jp == 0);
+              commit_both(V_EMPTY0 + stp);
+              commit_both(P_EMPTY);
+              FMLA_PTRACE_AT(gp, 5);
+            }
+            __syncwarp();
+            ++jp;
+            did = true;
+          } else if (js < nblk && (m & 0x18u) == 0x18u) {
+            tc::tc_fence_after();
+            if (lane == 0) FMLA_PTRACE_AT(gs, 2);
+            if (tc::elect_one()) {
+              if (sts == 0) s_block_pair<0>(tmem, desc_q, desc_k, idesc_s);
+              else s_block_pair<1>(tmem, desc_q, desc_k, idesc_s);
+              commit_both(S_FULL0 + sts);
+              commit_both(K_EMPTY0 + sts);
+              FMLA_PTRACE_AT(gs, 3);
+              if (js == nblk - 1) commit_both(Q_EMPTY);
+            }
+            __syncwarp();
+            ++js;
+            did = true;
+          }
+          if (did) {
+            idle = 0;
+          } else if (++idle > tc::kSpinLimit) {
+            if (lane == 0) tc::report_status(status, 106);
+            alive = false;
+          } else {
+            __nanosleep(20);
+          }
+        }
+        g += nblk;
+        if (alive && tc::elect_one()) commit_both(O_FULL);
+        __syncwarp();
+        ++req;
+      }
+    }
+  } else if (warp < 4) {
+    // ================================ softmax / epilogue ================================
+    const int r_row = tid & 63, th = tid >> 6;           // TMEM lane tid: row tid%64, token/column half tid/64
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t l_s_empty0 = lbar(S_EMPTY0), l_p_full = lbar(P_FULL), l_o_empty = lbar(O_EMPTY);
+    int g = 0, req = 0;
+    bool aborted = false;        // uniform over the 128 softmax threads: only read right after a bar_sync
+    for (int wi = 0; wi < tile.n_work; ++wi) {
+      const Work r = get_work<kDense>(P, tile, wi);
+      const int nblk = r.blk_hi - r.blk_lo;
+      float m_run = neg_inf();     // running maximum (base-2 scaled logits)
+      float m_used = 0.f;          // the maximum O and l are currently scaled with
+      float l_part = 0.f;          // this thread's share of the row sum
+      for (int j = 0; j < nblk && !aborted; ++j, ++g) {
+        const int st = g & 1;
+        uint32_t sv[32];
+        uint32_t vbits = 0xffffffffu;
+        if (tc::mbar_wait(bar(S_FULL0 + st), (g >> 1) & 1, status, 108)) {
+          if (tid == 0) FMLA_PTRACE_AT(g, 6);
+          tc::tc_fence_after();
+          tc::tmem_ld32(tmem + lane_addr + TMEM_S + st * 32, sv);
+          tc::tmem_wait_ld();
+          tc::tc_fence_before();
+        } else {
+          *sAbort = 1;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sv[i] = 0u;
+        }
+        tc::mbar_arrive_cluster(l_s_empty0 + st * 8);
+        if (tid == 0) FMLA_PTRACE_AT(g, 7);
+
+        const int tok0 = (r.blk_lo + j) * 64 + th * 32;
+        if (tok0 + 32 > r.border) vbits = tok0 >= r.border ? 0u : (0xffffffffu >> (32 - (r.border - tok0)));
+        if (vbits != 0xffffffffu) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (!((vbits >> i) & 1u)) sv[i] = 0xff800000u;
+        }
+        float mx4[4] = {neg_inf(), neg_inf(), neg_inf(), neg_inf()};
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+        float* xch = sMx + (j & 1) * 128;
+        xch[tid] = mx;
+        bar_sync(1, 128);
+        if (*sAbort) { aborted = true; break; }
+        mx = fmaxf(mx, xch[tid ^ 64]);
+        const float m_new = fmaxf(m_run, mx);
+
+        bool need = false;
+        if (j == 0 || (m_run == neg_inf() && m_new != neg_inf())) {
+          m_used = (m_new == neg_inf()) ? 0.f : m_new;      // O and l are exactly zero so far
+        } else {
+          need = (m_new - m_used) > kRescaleThreshold;
+        }
+        m_run = m_new;
+        const bool any_need = __any_sync(0xffffffffu, need);
+        bool pv_done = false;    // the previous P V must be complete before O is rescaled and before P is overwritten
+        if (any_need) {
+          if (!tc::mbar_wait(bar(P_EMPTY), (g & 1) ^ 1, status, 109)) *sAbort = 1;
+          pv_done = true;
+          const float m_next = need ? m_new : m_used;
+          const float alpha = exp2f(m_used - m_next);
+          m_used = m_next;
+          l_part *= alpha;
+          tc::tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            uint32_t ov[32];
+            tc::tmem_ld32(tmem + lane_addr + TMEM_O + c * 32, ov);
+            tc::tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tc::tmem_st32(tmem + lane_addr + TMEM_O + c * 32, ov);
+          }
+          tc::tmem_wait_st();
+          tc::tc_fence_before();
+        }
+        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = exp2f(fmaf(__uint_as_float(sv[2 * i]), scale_log2, -m_used));
+          const float p1 = exp2f(fmaf(__uint_as_float(sv[2 * i + 1]), scale_log2, -m_used));
+          rs4[i & 3] += p0 + p1;
+          pk[i] = pack_16x2<F16>(p0, p1);
+        }
+        l_part += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+        if (!pv_done && !tc::mbar_wait(bar(P_EMPTY), (g & 1) ^ 1, status, 109)) *sAbort = 1;
+        if (tid == 0) FMLA_PTRACE_AT(g, 9);
+        // P[row][th*32 .. +32) -> K-major 128B-swizzled A operand: 16-byte chunk (th*4 + q) ^ (row & 7)
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+          pst_shared_v4(sP + r_row * 128 + ((((th * 4 + q4) ^ (r_row & 7))) << 4),
+                        make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]));
+        tc::fence_proxy_async_smem();
+        tc::mbar_arrive_cluster(l_p_full);
+        if (tid == 0) FMLA_PTRACE_AT(g, 11);
+      }
+
+      // ---- epilogue of this work item ---------------------------------------------------
+      float* xch = sMx + 256;
+      bar_sync(1, 128);
+      xch[tid] = l_part;
+      bar_sync(1, 128);
+      if (*sAbort) aborted = true;
+      if (aborted) break;
+      const float l = l_part + xch[tid ^ 64];
+      const int head = tile.head0 + r_row;
+      const float inv = (l == 0.f || nblk == 0) ? 0.f : 1.f / l;
+      bool have_o = nblk > 0;
+      if (have_o) {
+        if (!tc::mbar_wait(bar(O_FULL), req & 1, status, 110)) { *sAbort = 1; have_o = false; }
+        tc::tc_fence_after();
+      }
+      const int q_seq_per_hk = p.s_q * p.hq_per_hk;
+      const int row_in_group = tile.sq * p.hq_per_hk + tile.hb * 64 + r_row;   // regrouped row index within the kv head
+      __nv_bfloat16* o_final = reinterpret_cast<__nv_bfloat16*>(p.out) + r.batch * p.o_stride_b + tile.sq * p.o_stride_s + head * p.o_stride_h;
+      const int64_t part_row = ((int64_t)r.split_slot * p.h_k + tile.kh) * q_seq_per_hk + row_in_group;
+      float* o_part = p.o_accum + part_row * 512;
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t ov[32];
+        if (have_o) {
+          tc::tmem_ld32(tmem + lane_addr + TMEM_O + c * 32, ov);
+          tc::tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = 0u;
+        }
+        const int col = (c >> 2) * 256 + th * 128 + (c & 3) * 32;
+        if (r.no_split) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 v;
+            v.x = pack_16x2<F16>(__uint_as_float(ov[q4 * 8 + 0]) * inv, __uint_as_float(ov[q4 * 8 + 1]) * inv);
+            v.y = pack_16x2<F16>(__uint_as_float(ov[q4 * 8 + 2]) * inv, __uint_as_float(ov[q4 * 8 + 3]) * inv);
+            v.z = pack_16x2<F16>(__uint_as_float(ov[q4 * 8 + 4]) * inv, __uint_as_float(ov[q4 * 8 + 5]) * inv);
+            v.w = pack_16x2<F16>(__uint_as_float(ov[q4 * 8 + 6]) * inv, __uint_as_float(ov[q4 * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(o_final + col + q4 * 8) = v;
+          }
+        } else {
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4) {
+            float4 v = make_float4(__uint_as_float(ov[q4 * 4 + 0]) * inv, __uint_as_float(ov[q4 * 4 + 1]) * inv,
+                                   __uint_as_float(ov[q4 * 4 + 2]) * inv, __uint_as_float(ov[q4 * 4 + 3]) * inv);
+            *reinterpret_cast<float4*>(o_part + col + q4 * 4) = v;
+          }
+        }
+      }
+      if (nblk > 0) {
+        tc::tc_fence_before();
+        tc::mbar_arrive_cluster(l_o_empty);
+        ++req;
+      }
+      if (th == 0) {
+        if (r.no_split) {
+          p.softmax_lse[((int64_t)r.batch * p.h_q + head) * p.s_q + tile.sq] = inv == 0.f ? pos_inf() : (log2f(l) + m_used) * kLn2;
+        } else {
+          p.lse_accum[part_row] = inv == 0.f ? neg_inf() : log2f(l) + m_used;
+        }
+      }
+    }
+  }
+
+  // neither CTA may leave (or give its tensor memory back) while its peer can still address it
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::cluster_sync_all();
+  if (warp == 5) tc::tmem_dealloc_pair(tmem, 512);
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn pair_encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess) f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+// 16-bit tensor [d3][d2][d1][d0=576] with element strides s1,s2,s3 ; box {64, b1, b2, 1}
+static bool pair_map_4d(CUtensorMap* m, const void* base, uint64_t d1, uint64_t d2, uint64_t d3, int64_t s1, int64_t s2, int64_t s3,
+                        uint32_t b1, uint32_t b2) {
+  EncodeTiledFn enc = pair_encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[4] = {576, d1, d2, d3};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(s1) * 2, static_cast<cuuint64_t>(s2) * 2, static_cast<cuuint64_t>(s3) * 2};
+  cuuint32_t box[4] = {64, b1, b2, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool decode_dense_pair_applies(const DecodeKernelParams& p) { return p.hq_per_hk % 128 == 0; }
+
+cudaError_t launch_decode_dense_pair(const DecodeKernelParams& p, cudaStream_t stream) {
+  TcParams P = {};
+  P.d = p;
+  CUtensorMap tq, tk, tv;
+  // q [b][s_q][h_q][576] ; box = 64 heads x 64 columns
+  if (!pair_map_4d(&tq, p.q, p.h_q, p.s_q, p.b, p.q_stride_h, p.q_stride_s, p.q_stride_b, 64, 1)) return cudaErrorInvalidValue;
+  // cache [num_blocks][64][h_k][576] addressed as (col, head, row-in-page, page): boxes of 32 rows (K part) and 64 rows (V part)
+  if (!pair_map_4d(&tk, p.kcache, p.h_k, 64, p.num_blocks, p.k_stride_head, p.k_stride_row, p.k_stride_block, 1, 32)) return cudaErrorInvalidValue;
+  if (!pair_map_4d(&tv, p.kcache, p.h_k, 64, p.num_blocks, p.k_stride_head, p.k_stride_row, p.k_stride_block, 1, 64)) return cudaErrorInvalidValue;
+  const int n_hb = p.hq_per_hk / 64;
+  const dim3 grid(p.s_q * n_hb, p.h_k, p.num_sm_parts);
+  static bool attr_set[2] = {false, false};      // idempotent, so a race between threads is harmless
+  if (p.is_f16) {
+    auto kern = mla_pair_kernel<true>;
+    if (!attr_set[1]) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ptc::SMEM_BYTES);
+      if (e != cudaSuccess) return e;
+      attr_set[1] = true;
+    }
+    kern<<<grid, ptc::kThreads, ptc::SMEM_BYTES, stream>>>(P, tq, tk, tv);
+  } else {
+    auto kern = mla_pair_kernel<false>;
+    if (!attr_set[0]) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ptc::SMEM_BYTES);
+      if (e != cudaSuccess) return e;
+      attr_set[0] = true;
+    }
+    kern<<<grid, ptc::kThreads, ptc::SMEM_BYTES, stream>>>(P, tq, tk, tv);
+  }
+  return cudaGetLastError();
+}
+
+#ifdef FMLA_TRACE
+extern "C" int fmla_debug_read_pair_trace(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_pair_trace, sizeof(long long) * n);
+}
+#endif
+
+cudaError_t set_status_mirror_pair(int* mapped_host_word) { return tc::set_status_mirror(mapped_host_word); }
+
+cudaError_t read_decode_pair_status(int* host_status, bool reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(host_status, g_decode_pair_status, sizeof(int));
+  if (e != cudaSuccess) return e;
+  if (reset && *host_status != 0) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_decode_pair_status, &zero, sizeof(int));
+  }
+  return e;
+}
+
+}  // namespace fmla

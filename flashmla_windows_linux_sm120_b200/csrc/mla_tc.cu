@@ -28,19 +28,15 @@
 // Every mbarrier wait is bounded (tc_common.cuh); a pipeline fault sets a status word and lets the
 // CTA drain and free its tensor memory.
 #include "kernels.h"
+#include "mla_work.cuh"
 #include "tc_common.cuh"
 
 #include <cuda.h>
 #include <cuda_fp8.h>
 
+#include <cstdlib>
+
 namespace fmla {
-
-enum TcMode { kDense = 0, kSparseDecode = 1, kSparsePrefill = 2 };
-
-struct TcParams {
-  DecodeKernelParams d;          // decode modes
-  SparsePrefillKernelParams sp;  // prefill mode
-};
 
 namespace dtc {
 constexpr int kChunkBytes = 64 * 128;             // [64 rows x 64 bf16], 128-byte rows
@@ -77,88 +73,6 @@ __device__ long long g_decode_trace[64 * 16];
 #else
 #define FMLA_TRACE_AT(blk, slot) do {} while (0)
 #endif
-
-// One unit of work of a CTA: a request (decode) or a query token (prefill) and the range of
-// 64-token blocks of its key list that this CTA covers.
-struct Work {
-  int batch;                 // request index (decode) / query token (prefill)
-  int blk_lo, blk_hi;
-  int seqlen, border;        // dense: cached tokens, first masked token
-  int split_slot;
-  bool no_split;
-  const int* idx;            // sparse: the index list of this (request, query token)
-};
-
-// Which tile and which stretch of the schedule a CTA owns.
-struct Tile {
-  int sq, hb, kh, head0, nvalid;
-  int begin_idx, end_idx, begin_block, end_block, begin_split;
-  int n_work;
-};
-
-template <int MODE>
-__device__ __forceinline__ Tile make_tile(const TcParams& P) {
-  Tile t;
-  if constexpr (MODE == kSparsePrefill) {
-    // persistent over query tokens: this CTA takes tokens blockIdx.y, blockIdx.y + gridDim.y, ... so that the
-    // Q load and the output stores of one token overlap with the blocks of its neighbours
-    t.hb = blockIdx.x; t.sq = blockIdx.y; t.kh = 0;
-    t.head0 = t.hb * 64; t.nvalid = 64;
-    t.begin_idx = t.end_idx = 0; t.begin_block = 0; t.end_block = P.sp.topk / 64; t.begin_split = 0;
-    t.n_work = (P.sp.s_q - static_cast<int>(blockIdx.y) + static_cast<int>(gridDim.y) - 1) / static_cast<int>(gridDim.y);
-  } else {
-    const DecodeKernelParams& p = P.d;
-    int part;
-    if constexpr (MODE == kDense) {
-      const int n_hb = (p.hq_per_hk + 63) >> 6;
-      t.sq = blockIdx.x / n_hb; t.hb = blockIdx.x % n_hb; t.kh = blockIdx.y; part = blockIdx.z;
-    } else {
-      t.hb = blockIdx.x; t.sq = blockIdx.y; t.kh = 0; part = blockIdx.z;
-    }
-    t.head0 = t.kh * p.hq_per_hk + t.hb * 64;
-    t.nvalid = min(64, p.hq_per_hk - t.hb * 64);
-    const int4 md = __ldg(reinterpret_cast<const int4*>(p.tile_scheduler_metadata + part * 8));
-    t.begin_idx = md.x; t.begin_block = md.y; t.end_idx = md.z; t.end_block = md.w;
-    t.begin_split = __ldg(p.tile_scheduler_metadata + part * 8 + 4);
-    t.n_work = t.begin_idx >= p.b ? 0 : t.end_idx - t.begin_idx + 1;
-  }
-  return t;
-}
-
-template <int MODE>
-__device__ __forceinline__ Work get_work(const TcParams& P, const Tile& t, int i) {
-  Work w;
-  if constexpr (MODE == kSparsePrefill) {
-    w.batch = t.sq + i * static_cast<int>(gridDim.y);          // the query token
-    w.blk_lo = 0; w.blk_hi = P.sp.topk / 64;
-    w.seqlen = P.sp.topk; w.border = P.sp.topk;
-    w.split_slot = 0; w.no_split = true;
-    w.idx = P.sp.indices + (int64_t)w.batch * P.sp.indices_stride_s;
-  } else {
-    const DecodeKernelParams& p = P.d;
-    const int batch = t.begin_idx + i;
-    w.batch = batch;
-    int nblk_total, nblk_visible;
-    if constexpr (MODE == kDense) {
-      w.seqlen = __ldg(p.seqlens_k + batch);
-      nblk_total = (w.seqlen + 63) >> 6;
-      w.border = p.is_causal ? w.seqlen - (p.s_q - 1 - t.sq) : w.seqlen;
-      nblk_visible = w.border > 0 ? (w.border + 63) >> 6 : 0;
-      w.idx = nullptr;
-    } else {
-      w.seqlen = p.topk; w.border = p.topk;
-      nblk_total = nblk_visible = p.topk >> 6;
-      w.idx = p.indices + batch * p.indices_stride_b + t.sq * p.indices_stride_s;
-    }
-    w.blk_lo = batch == t.begin_idx ? t.begin_block : 0;
-    w.blk_hi = min(min(batch == t.end_idx ? t.end_block : nblk_total, nblk_total), nblk_visible);
-    if (w.blk_hi < w.blk_lo) w.blk_hi = w.blk_lo;
-    const int lo = __ldg(p.num_splits + batch);
-    w.no_split = !p.force_partial && __ldg(p.num_splits + batch + 1) - lo == 1;
-    w.split_slot = lo + (batch == t.begin_idx ? t.begin_split : 0);
-  }
-  return w;
-}
 
 // 16-byte chunk c16 (0..71) of row r of a stage -> byte offset in the TMA-compatible layout
 __device__ __forceinline__ uint32_t stage_off(int r, int c16) {
@@ -212,7 +126,7 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
   const Tile tile = make_tile<MODE>(P);
   if (tile.n_work == 0) return;
   if ((sbase & 1023u) != 0) {   // the swizzled tiles need a 1024-byte aligned base
-    if (tid == 0) atomicCAS(status, 0, 30);
+    if (tid == 0) tc::report_status(status, 30);
     return;
   }
   const float scale_log2 = MODE == kSparsePrefill ? P.sp.scale_log2 : p.scale_log2;
@@ -522,7 +436,7 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
         if (did) {
           idle = 0;
         } else if (++idle > tc::kSpinLimit) {
-          if (lane == 0) atomicCAS(status, 0, 6);
+          if (lane == 0) tc::report_status(status, 6);
           alive = false;
         } else {
           __nanosleep(20);   // a tight poll would take issue slots from the softmax warp on this scheduler
@@ -590,10 +504,12 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
         // O and l carry the scale 2^-m_used; it is moved only when the maximum grew by more than the
         // threshold (or when the first real value arrives after fully masked blocks)
         bool need = false;
-        if (j == 0) {
+        if (j == 0 || (m_run == neg_inf() && m_new != neg_inf())) {
+          // first block, or the first visible key after fully masked blocks: O and l are exactly zero, so the
+          // reference scale is simply set (multiplying 0 by 2^(0 - m_new) would give NaN for m_new < -128)
           m_used = (m_new == neg_inf()) ? 0.f : m_new;
         } else {
-          need = (m_new - m_used) > kRescaleThreshold || (m_run == neg_inf() && m_new != neg_inf());
+          need = (m_new - m_used) > kRescaleThreshold;
         }
         m_run = m_new;
         const bool any_need = __any_sync(0xffffffffu, need);
@@ -763,7 +679,17 @@ static cudaError_t launch_tc(const TcParams& P, const CUtensorMap& tq, const CUt
   return cudaGetLastError();
 }
 
+// FMLA_DISABLE_PAIR=1 in the environment keeps the one-CTA-per-64-heads kernel for every shape (A/B runs)
+static bool pair_kernel_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("FMLA_DISABLE_PAIR");
+    return !(v && v[0] == '1');
+  }();
+  return on;
+}
+
 cudaError_t launch_decode_dense_tc(const DecodeKernelParams& p, cudaStream_t stream) {
+  if (decode_dense_pair_applies(p) && pair_kernel_enabled()) return launch_decode_dense_pair(p, stream);
   TcParams P = {};
   P.d = p;
   CUtensorMap tq, tkv;
@@ -805,6 +731,8 @@ extern "C" int fmla_debug_read_trace(long long* host, int n) {
   return (int)cudaMemcpyFromSymbol(host, g_decode_trace, sizeof(long long) * n);
 }
 #endif
+
+cudaError_t set_status_mirror_mla(int* mapped_host_word) { return tc::set_status_mirror(mapped_host_word); }
 
 cudaError_t read_decode_tc_status(int* host_status, bool reset) {
   cudaError_t e = cudaMemcpyFromSymbol(host_status, g_decode_tc_status, sizeof(int));

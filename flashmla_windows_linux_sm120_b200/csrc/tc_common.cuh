@@ -17,6 +17,22 @@ namespace tc {
 
 constexpr int kSpinLimit = 1 << 20;   // mbarrier.try_wait polls (each poll blocks up to the HW time slice)
 
+// Where an expired wait is reported: the translation unit's own status word in device memory, and (once
+// the host has registered it) a word in host memory that the GPU writes through a mapped pointer, so
+// that the next library call can see the failure without synchronising.  One pointer per translation unit.
+static __device__ int* g_status_mirror = nullptr;
+static inline cudaError_t set_status_mirror(int* mapped_host_word) {
+  return cudaMemcpyToSymbol(g_status_mirror, &mapped_host_word, sizeof(mapped_host_word));
+}
+__device__ __forceinline__ void report_status(int* status, int code) {
+  if (status) atomicCAS(status, 0, code);
+  int* m = g_status_mirror;
+  if (m) {
+    *reinterpret_cast<volatile int*>(m) = code;
+    __threadfence_system();
+  }
+}
+
 // ---- mbarrier -------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
@@ -53,7 +69,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
   for (int i = 0; i < kSpinLimit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
-  if (status) atomicCAS(status, 0, code);
+  report_status(status, code);
   return false;
 }
 
@@ -66,7 +82,7 @@ __device__ __forceinline__ bool mbar_wait2(uint32_t bar_a, uint32_t par_a, uint3
     const bool hit = lane < 2 && mbar_test_wait(b, pp);
     if ((__ballot_sync(0xffffffffu, hit) & 3u) == 3u) return true;
   }
-  if (status && lane == 0) atomicCAS(status, 0, code);
+  if (lane == 0) report_status(status, code);
   return false;
 }
 
@@ -152,6 +168,84 @@ __device__ __forceinline__ void mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_
 __device__ __forceinline__ void mma_ws_ss(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.ws.cta_group::1.kind::f16 [%0], %1, %2, %3, p, 0;\n}\n" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+
+// ---- CTA pairs (cluster of two CTAs, tcgen05 cta_group::2) ---------------------------------------------
+// One thread of the leader CTA (cluster rank 0) issues MMAs that run on the tensor cores of both SMs: M = 128
+// means 64 accumulator rows per CTA, the A operand comes from each CTA's own shared memory and the B operand
+// is split along N (first half from the leader's shared memory, second half from its peer's), at the same
+// shared-memory offsets in both CTAs.  No multicast anywhere: a commit or a copy names one barrier of one CTA.
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the variable at `addr` (shared::cta) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// arrivals on a barrier that may live in the other CTA of the cluster
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;\n" ::"r"(cluster_bar), "r"(bytes) : "memory");
+}
+// wait on a barrier of this CTA whose arrivals come from both CTAs (acquire at cluster scope)
+__device__ __forceinline__ bool mbar_test_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* status, int code) {
+  for (int i = 0; i < kSpinLimit; ++i)
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+  report_status(status, code);
+  return false;
+}
+// 4-D tile load into this CTA's shared memory whose completion is counted on a barrier that may live in the
+// other CTA of the pair (given as a shared::cluster address)
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3, uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n" ::"r"(dst),
+      "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(cluster_bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result_addr, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_result_addr), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// arrive on ONE barrier (shared::cluster address: this CTA's or the peer's) once every MMA issued so far has completed
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void mma_pair_ss(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
       "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
       : "memory");
 }

@@ -80,22 +80,43 @@ def shard_kv_pages(seqlen: int, world_size: int, block: int = 64) -> List[Tuple[
 # KV-sharded decode
 # ---------------------------------------------------------------------------------------------------
 class PartialBuffers:
-    """N slots of (partial O [rows, 512] fp32, base-2 LSE [rows] fp32, flag uint32) living on one GPU."""
+    """Two sets (selected by the parity of the step's epoch) of N slots of (partial O [rows, 512] fp32,
+    base-2 LSE [rows] fp32, flag uint32) living on one GPU.
+
+    Why two sets: a rank may start the push of step e+1 as soon as its own merge of step e is done, which
+    only needs the peers' pushes of step e, not their merges.  With one set it could overwrite a slot that a
+    slower peer has not merged yet.  With two, the push of step e+2 (the next one into the same set) comes
+    after this rank's merge of e+1, which waited for the peer's push of e+1, which the peer's stream ordered
+    after its merge of e: the slot is free by construction, without any extra flag.
+    """
 
     def __init__(self, num_slots: int, rows: int, device, tensors=None):
         self.num_slots, self.rows = num_slots, rows
         if tensors is None:
-            o = torch.zeros((num_slots, rows, 512), dtype=torch.float32, device=device)
-            lse = torch.zeros((num_slots, rows), dtype=torch.float32, device=device)
-            flags = torch.zeros((num_slots,), dtype=torch.int32, device=device)
+            o = torch.zeros((2, num_slots, rows, 512), dtype=torch.float32, device=device)
+            lse = torch.zeros((2, num_slots, rows), dtype=torch.float32, device=device)
+            flags = torch.zeros((2, num_slots), dtype=torch.int32, device=device)
             tensors = (o, lse, flags)
         self.o, self.lse, self.flags = tensors
+
+    def offsets(self, epoch: int) -> Tuple[int, int, int]:
+        """Byte offsets of the set used by `epoch` inside the o / lse / flags allocations."""
+        par = epoch & 1
+        return (par * self.num_slots * self.rows * 512 * 4, par * self.num_slots * self.rows * 4, par * self.num_slots * 4)
+
+    def ptrs(self, epoch: int, bases: Optional[Tuple[int, int, int]] = None) -> Tuple[int, int, int]:
+        """Device addresses of the set used by `epoch`; `bases` = the allocations' addresses as another rank sees them."""
+        if bases is None:
+            bases = (self.o.data_ptr(), self.lse.data_ptr(), self.flags.data_ptr())
+        off = self.offsets(epoch)
+        return (bases[0] + off[0], bases[1] + off[1], bases[2] + off[2])
 
 
 def push_partial(q, k_cache, block_table, cache_seqlens, tile_scheduler_metadata, num_splits, softmax_scale,
                  slot: int, dst_ptrs: Sequence[Tuple[int, int, int]], epoch: int, counter: torch.Tensor) -> None:
     """Dense decode over the local shard; the merged partial goes to slot `slot` of every destination
-    given as (o_ptr, lse_ptr, flag_ptr) device addresses."""
+    given as (o_ptr, lse_ptr, flag_ptr) device addresses of the buffer set of this epoch
+    (`PartialBuffers.ptrs(epoch, ...)`)."""
     from ._cabi import DecodeParams, PeerPush, check, lib
     b, s_q, h_q, d = q.shape
     num_blocks, page, h_k, _ = k_cache.shape
@@ -125,15 +146,17 @@ def push_partial(q, k_cache, block_table, cache_seqlens, tile_scheduler_metadata
 
 
 def merge_partials(buf: PartialBuffers, epoch: int, max_polls: int = 5_000_000):
-    """Waits (bounded) for all slots of `buf` to carry `epoch`, merges them.  Returns (out bf16 [rows,512],
-    lse fp32 [rows] natural log)."""
+    """Waits (bounded) for all slots of the buffer set of `epoch` to carry `epoch`, merges them.  Returns
+    (out bf16 [rows,512], lse fp32 [rows] natural log).  If the wait runs out the outputs are not written; the
+    condition is reported by `fmla_device_status` and by the next library call on this device."""
     from ._cabi import check, lib
     dev = buf.o.device
+    po, pl, pf = buf.ptrs(epoch)
     with torch.cuda.device(dev):
         out = torch.empty((buf.rows, 512), dtype=torch.bfloat16, device=dev)
         lse = torch.empty((buf.rows,), dtype=torch.float32, device=dev)
-        check(lib.fmla_merge_peer_partials(buf.lse.data_ptr(), buf.o.data_ptr(), buf.num_slots, buf.rows, 512,
-                                           buf.flags.data_ptr(), epoch, max_polls, out.data_ptr(), 512, lse.data_ptr(),
+        check(lib.fmla_merge_peer_partials(pl, po, buf.num_slots, buf.rows, 512, pf, epoch, max_polls,
+                                           out.data_ptr(), 512, lse.data_ptr(),
                                            torch.cuda.current_stream(dev).cuda_stream))
     return out, lse
 
@@ -159,15 +182,15 @@ class KVShardedDecode:
             import torch.distributed._symmetric_memory as symm
             n = self.world
             # one symmetric allocation per array: every rank can address every peer's copy
-            self._o = symm.empty((n, self.rows, 512), dtype=torch.float32, device=device)
-            self._lse = symm.empty((n, self.rows), dtype=torch.float32, device=device)
-            self._flags = symm.empty((n,), dtype=torch.int32, device=device)
+            self._o = symm.empty((2, n, self.rows, 512), dtype=torch.float32, device=device)
+            self._lse = symm.empty((2, n, self.rows), dtype=torch.float32, device=device)
+            self._flags = symm.empty((2, n), dtype=torch.int32, device=device)
             self._flags.zero_()
             gname = group.group_name if group is not None else dist.group.WORLD.group_name
             self._h = [symm.rendezvous(t, gname) for t in (self._o, self._lse, self._flags)]
             self.buf = PartialBuffers(n, self.rows, device, (self._o, self._lse, self._flags))
-            self.dst_ptrs = [(int(self._h[0].buffer_ptrs[r]), int(self._h[1].buffer_ptrs[r]), int(self._h[2].buffer_ptrs[r]))
-                             for r in range(n)]
+            self.peer_bases = [(int(self._h[0].buffer_ptrs[r]), int(self._h[1].buffer_ptrs[r]), int(self._h[2].buffer_ptrs[r]))
+                               for r in range(n)]
             torch.cuda.synchronize(device)
             dist.barrier(group)
         else:
@@ -183,16 +206,18 @@ class KVShardedDecode:
         md, ns = get_mla_metadata(cache_seqlens, s_q * h_q // k_cache.shape[2], k_cache.shape[2])
         self.epoch += 1
         if self.transport == "peer":
-            push_partial(q, k_cache, block_table, cache_seqlens, md, ns, softmax_scale, self.rank, self.dst_ptrs,
+            dst = [self.buf.ptrs(self.epoch, bases) for bases in self.peer_bases]
+            push_partial(q, k_cache, block_table, cache_seqlens, md, ns, softmax_scale, self.rank, dst,
                          self.epoch, self.counter)
             out, lse = merge_partials(self.buf, self.epoch)
         else:
             loc = self.local
+            par = self.epoch & 1
             push_partial(q, k_cache, block_table, cache_seqlens, md, ns, softmax_scale, 0,
-                         [(loc.o.data_ptr(), loc.lse.data_ptr(), loc.flags.data_ptr())], self.epoch, self.counter)
-            self.dist.all_gather_into_tensor(self.buf.o, loc.o[0], group=self.group)
-            self.dist.all_gather_into_tensor(self.buf.lse, loc.lse[0], group=self.group)
-            self.buf.flags.fill_(self.epoch)
+                         [loc.ptrs(self.epoch)], self.epoch, self.counter)
+            self.dist.all_gather_into_tensor(self.buf.o[par], loc.o[par, 0], group=self.group)
+            self.dist.all_gather_into_tensor(self.buf.lse[par], loc.lse[par, 0], group=self.group)
+            self.buf.flags[par].fill_(self.epoch)
             out, lse = merge_partials(self.buf, self.epoch)
         # rows are ordered (batch, head): regrouped row index of a kv head == head for s_q == 1, h_k == 1
         return out.view(b, 1, h_q, 512), lse.view(b, h_q, 1)

@@ -274,7 +274,15 @@ int fmla_quantize_kv_fp8(const void* kv_bf16, int64_t kv_stride_row, int num_tok
  * kernels set when one of their bounded waits (mbarrier polls) gives up instead
  * of hanging: 0 = no fault.  Returns FMLA_ERR_DEVICE_TIMEOUT when it is non-zero;
  * `reset` != 0 clears it.  The reference has no counterpart: its kernels wait
- * without bound and trap on failed asserts (csrc/utils.h:24-30). */
+ * without bound and trap on failed asserts (csrc/utils.h:24-30).
+ *
+ * A kernel that gives up also stores the code into a page of host memory that the
+ * library registers (page-locked, mapped) the first time a launching entry point
+ * runs in the process; every launching entry point reads that word on entry,
+ * without synchronising, and returns FMLA_ERR_DEVICE_TIMEOUT instead of launching
+ * on top of a failed pipeline until the condition is cleared with `reset`.  That
+ * first call does one-time set-up per device (a host-memory registration and a few
+ * symbol updates) and therefore has to come before any stream capture. */
 int fmla_device_status(int* status_host, int reset);
 
 /* sizeof() of the parameter blocks as compiled into the library, so a foreign

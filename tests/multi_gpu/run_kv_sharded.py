@@ -54,6 +54,13 @@ def main():
         results[transport] = (out.clone(), lse.clone(), float(t))
         dist.barrier()
 
+    # no bounded wait may have run out on any rank during the unsynchronised steps above
+    import ctypes
+    from flashmla_windows_linux_sm120_b200._cabi import lib
+    st = ctypes.c_int(0)
+    rc = lib.fmla_device_status(ctypes.byref(st), 1)
+    assert rc == 0 and st.value == 0, f"rank {rank}: device status {st.value}"
+
     o_p, l_p, t_p = results["peer"]
     o_n, l_n, t_n = results["nccl"]
     assert torch.equal(o_p, o_n) and torch.equal(l_p, l_n), "peer-memory merge and NCCL baseline disagree"

@@ -5,7 +5,9 @@ plugin's enqueue hook, work recorded into a stream) uses this entry point instea
 fmla_fwd_kvcache_mla; the partial-result scratch then comes from arrays built into the library.
 The test drives it through the C ABI, twice in a row with different problems (the second run sees
 whatever the first left in the shared arrays), and checks each result against the regular entry
-point fed with caller-allocated scratch.  Collected last on purpose (file name), so a failure here
+point fed with caller-allocated scratch: the two run the same kernels on the same schedule in a fixed
+order, so the results have to be bit-identical; one of the two problems is also checked against the
+CPU oracle.  Collected last on purpose (file name), so a failure here
 cannot hide a failure elsewhere under `pytest -x`.
 """
 import ctypes as C
@@ -64,16 +66,20 @@ def _run_both(t):
     pb = _params(d, t, md, ns, out_b, lse_b, None, None)        # no scratch pointers at all
     check(lib.fmla_fwd_kvcache_mla_static_scratch(C.byref(pb), stream))
     torch.cuda.synchronize()
-    return (out_a.cpu(), lse_a.cpu()), (out_b.cpu(), lse_b.cpu())
+    return data, (out_a.cpu(), lse_a.cpu()), (out_b.cpu(), lse_b.cpu())
 
 
 def test_static_scratch_matches_regular_entry_point_twice_in_a_row():
     cases = [gen.DecodeCase(b=3, s_q=2, s_k=3000, is_varlen=True, is_causal=True, h_q=128, seed=11),
              gen.DecodeCase(b=2, s_q=1, s_k=1500, is_varlen=True, is_causal=False, h_q=64, seed=12)]
-    for t in cases:
-        (out_a, lse_a), (out_b, lse_b) = _run_both(t)
+    from oracle import decode
+    for n, t in enumerate(cases):
+        data, (out_a, lse_a), (out_b, lse_b) = _run_both(t)
         assert not torch.isnan(out_b.float()).any() and not torch.isnan(lse_b).any()
-        U.assert_out_lse(out_b, lse_b, out_a, lse_a)      # same tolerances as the decode parity tests
+        assert torch.equal(out_b, out_a) and torch.equal(lse_b, lse_a)
+        if n == 0:
+            ref_out, ref_lse = decode.decode_ref(data.cache_seqlens, data.block_table, data.q, data.blocked_k, 512, t.is_causal)
+            U.assert_out_lse(out_b, lse_b, ref_out, ref_lse, what="static scratch vs oracle")
 
 
 def test_static_scratch_rejects_oversized_problems():
