@@ -37,6 +37,7 @@ struct DecodeKernelParams {
   int is_f16;                  // q, cache and out are fp16 instead of bf16 (dense decode only)
   int indices_logical;         // sparse decode: indices are token positions, mapped through block_table in the kernel
   int force_partial;
+  int l2_prefetch_dist;        // pair kernel: cache pages this many blocks ahead are pulled into L2 (0 = off)
   int push_slot, push_num_dst;
   float* push_o[8];            // [num_slots][b * h_k * rows][512]
   float* push_lse[8];          // [num_slots][b * h_k * rows], base 2

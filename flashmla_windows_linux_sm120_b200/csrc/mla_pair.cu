@@ -32,6 +32,8 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
+
 namespace fmla {
 
 namespace ptc {
@@ -43,15 +45,26 @@ constexpr int kVStageBytes = 4 * kChunkBytes;     // 32 768: 64 tokens x 256 val
 constexpr int Q_OFF = 0;
 constexpr int K_OFF = Q_OFF + kQBytes;            // 2 stages
 constexpr int V_OFF = K_OFF + 2 * kKStageBytes;   // 2 stages
-constexpr int P_OFF = V_OFF + 2 * kVStageBytes;   // [64 x 64]
-constexpr int BAR_OFF = P_OFF + kChunkBytes;
+constexpr int P_OFF = V_OFF + 2 * kVStageBytes;   // 2 x [64 x 64]
+constexpr int BAR_OFF = P_OFF + 2 * kChunkBytes;
 constexpr int MX_OFF = BAR_OFF + 256;             // float [3][128] exchange
 constexpr int MISC_OFF = MX_OFF + 1536;
 constexpr int SMEM_BYTES = MISC_OFF + 64;
 // leader-side barriers (waited on by the MMA warp of rank 0; arrivals come from both CTAs)
 // and per-CTA barriers (each CTA waits on its own copy; the leader's commits arrive on both copies)
-enum Bar { Q_FULL = 0, K_FULL0, K_FULL1, V_FULL0, V_FULL1, S_EMPTY0, S_EMPTY1, P_FULL, O_EMPTY,
-           Q_EMPTY, K_EMPTY0, K_EMPTY1, V_EMPTY0, V_EMPTY1, V_LAND0, V_LAND1, S_FULL0, S_FULL1, P_EMPTY, O_FULL, NUM_BARS };
+// The K part of a block can be handled in kKGroups groups of column chunks, each with its own full / empty
+// barrier (a group is refilled as soon as the S instructions that read it have completed).  Measured on the
+// benchmark shape: 3 groups stretch S over the arrival of its last group and nearly double the step
+// (3150 instead of 1810 clocks per block), so one group is used.
+#ifndef FMLA_PAIR_KGROUPS
+#define FMLA_PAIR_KGROUPS 1
+#endif
+constexpr int kKGroups = FMLA_PAIR_KGROUPS;
+constexpr int kChunksPerGroup = 9 / kKGroups;
+static_assert(kKGroups == 1 || kKGroups == 3, "9 column chunks split into 1 or 3 groups");
+enum Bar { Q_FULL = 0, K_FULL0, K_FULL_END = K_FULL0 + 2 * kKGroups - 1, V_FULL0, V_FULL1, S_EMPTY0, S_EMPTY1, P_FULL0, P_FULL1, O_EMPTY,
+           Q_EMPTY, K_EMPTY0, K_EMPTY_END = K_EMPTY0 + 2 * kKGroups - 1, V_EMPTY0, V_EMPTY1, V_LAND0, V_LAND1, S_FULL0, S_FULL1,
+           P_EMPTY0, P_EMPTY1, O_FULL, NUM_BARS };
 constexpr int TMEM_O = 0, TMEM_S = 256;
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory limit per CTA");
 static_assert(NUM_BARS * 8 <= 256, "barrier area too small");
@@ -62,11 +75,15 @@ constexpr int kThreads = 256;
 __device__ int g_decode_pair_status = 0;
 
 #ifdef FMLA_TRACE
-__device__ long long g_pair_trace[64 * 16];
+__device__ long long g_pair_trace[160 * 16];
+__device__ long long g_pair_span[512 * 2];       // per CTA: first and last clock (globaltimer would be comparable across SMs)
 #define FMLA_PTRACE_AT(blk, slot)                                                          \
   do {                                                                                      \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (blk) < 64) g_pair_trace[(blk) * 16 + (slot)] = clock64(); \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == FMLA_TRACE_PART && (blk) < 160) g_pair_trace[(blk) * 16 + (slot)] = clock64(); \
   } while (0)
+#ifndef FMLA_TRACE_PART
+#define FMLA_TRACE_PART 0
+#endif
 #else
 #define FMLA_PTRACE_AT(blk, slot) do {} while (0)
 #endif
@@ -75,12 +92,13 @@ __device__ __forceinline__ void pst_shared_v4(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// The 36 S instructions of one block in stage ST: descriptors are a warp-uniform base plus an immediate.
-template <int ST>
-__device__ __forceinline__ void s_block_pair(uint32_t tmem, uint64_t desc_q, uint64_t desc_k, uint32_t idesc) {
+// The S instructions of column-chunk group GRP of one block in stage ST: descriptors are a warp-uniform base
+// plus an immediate.
+template <int ST, int GRP>
+__device__ __forceinline__ void s_group_pair(uint32_t tmem, uint64_t desc_q, uint64_t desc_k, uint32_t idesc) {
   using namespace ptc;
 #pragma unroll
-  for (int c = 0; c < 9; ++c)
+  for (int c = kChunksPerGroup * GRP; c < kChunksPerGroup * (GRP + 1); ++c)
 #pragma unroll
     for (int s = 0; s < 4; ++s)
       tc::mma_pair_ss(tmem + TMEM_S + ST * 32, tc::desc_advance(desc_q, c * kChunkBytes + s * 32),
@@ -93,7 +111,7 @@ __device__ __forceinline__ void pv_block_pair(uint32_t tmem, uint64_t desc_p, ui
   for (int h = 0; h < 2; ++h)
 #pragma unroll
     for (int s = 0; s < 4; ++s)
-      tc::mma_pair_ss(tmem + TMEM_O + h * 128, tc::desc_advance(desc_p, s * 32),
+      tc::mma_pair_ss(tmem + TMEM_O + h * 128, tc::desc_advance(desc_p, ST * kChunkBytes + s * 32),
                       tc::desc_advance(desc_v, ST * kVStageBytes + h * 2 * kChunkBytes + s * 2048), idesc, (first && s == 0) ? 0u : 1u);
 }
 
@@ -115,6 +133,13 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = tc::cluster_rank();
+#ifdef FMLA_TRACE
+  if (tid == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_pair_span[(blockIdx.z * gridDim.x + blockIdx.x) * 2] = (long long)t;
+  }
+#endif
   const Tile tile = make_tile<kDense>(P);
   if (tile.n_work == 0) return;                 // both CTAs of a pair see the same schedule row
   const bool misaligned = (sbase & 1023u) != 0;  // the swizzled tiles need a 1024-byte aligned base
@@ -123,13 +148,13 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
 
   if (tid == 0) {
     tc::mbar_init(bar(Q_FULL), 2);
-    tc::mbar_init(bar(K_FULL0), 2);
-    tc::mbar_init(bar(K_FULL1), 2);
+    for (int i = K_FULL0; i <= K_FULL_END; ++i) tc::mbar_init(bar(i), 2);
     tc::mbar_init(bar(V_FULL0), 2);
     tc::mbar_init(bar(V_FULL1), 2);
     tc::mbar_init(bar(S_EMPTY0), 256);
     tc::mbar_init(bar(S_EMPTY1), 256);
-    tc::mbar_init(bar(P_FULL), 256);
+    tc::mbar_init(bar(P_FULL0), 256);
+    tc::mbar_init(bar(P_FULL1), 256);
     tc::mbar_init(bar(O_EMPTY), 256);
     for (int i = Q_EMPTY; i < NUM_BARS; ++i) tc::mbar_init(bar(i), 1);
     tc::fence_mbar_init();
@@ -161,18 +186,38 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
 #pragma unroll
         for (int c = 0; c < 9; ++c) tc::tma_load_4d_pair(sQ + c * kChunkBytes, &tmap_q, c * 64, tile.head0, tile.sq, r.batch, lbar(Q_FULL));
         const int* bt = p.block_table + r.batch * p.block_table_stride_b;
+        const int pf = p.l2_prefetch_dist;
+        // the leader pulls whole pages into L2 `pf` blocks ahead of the loads of both CTAs (the V parts use the
+        // 64-row map, whose boxes cover a page in 9 pieces)
+        if (pf > 0 && rank == 0) {
+          for (int blk = r.blk_lo; blk < min(r.blk_lo + pf, r.blk_hi); ++blk) {
+            const int pg = __ldg(bt + blk);
+#pragma unroll
+            for (int c = 0; c < 9; ++c) tc::tma_prefetch_l2_4d(&tmap_v64, c * 64, tile.kh, 0, pg);
+          }
+        }
         int page_next = __ldg(bt + r.blk_lo);
         for (int blk = r.blk_lo; blk < r.blk_hi; ++blk, ++g) {
           const int st = g & 1;
           const int page = page_next;
           if (blk + 1 < r.blk_hi) page_next = __ldg(bt + blk + 1);
-          alive = tc::mbar_wait(bar(K_EMPTY0 + st), ((g >> 1) & 1) ^ 1, status, 102);
-          if (!alive) break;
-          FMLA_PTRACE_AT(g, 0);
-          tc::mbar_arrive_expect_tx_cluster(lbar(K_FULL0 + st), kKStageBytes);
+          if (pf > 0 && rank == 0 && blk + pf < r.blk_hi) {
+            const int pg = __ldg(bt + blk + pf);
 #pragma unroll
-          for (int c = 0; c < 9; ++c)
-            tc::tma_load_4d_pair(sK + st * kKStageBytes + c * kKChunkBytes, &tmap_k32, c * 64, tile.kh, 32 * static_cast<int>(rank), page, lbar(K_FULL0 + st));
+            for (int c = 0; c < 9; ++c) tc::tma_prefetch_l2_4d(&tmap_v64, c * 64, tile.kh, 0, pg);
+          }
+#pragma unroll
+          for (int grp = 0; grp < kKGroups; ++grp) {
+            alive = alive && tc::mbar_wait(bar(K_EMPTY0 + st * kKGroups + grp), ((g >> 1) & 1) ^ 1, status, 102);
+            if (!alive) break;
+            if (grp == 0) FMLA_PTRACE_AT(g, 0);
+            const uint32_t full = lbar(K_FULL0 + st * kKGroups + grp);
+            tc::mbar_arrive_expect_tx_cluster(full, kChunksPerGroup * kKChunkBytes);
+#pragma unroll
+            for (int c = kChunksPerGroup * grp; c < kChunksPerGroup * (grp + 1); ++c)
+              tc::tma_load_4d_pair(sK + st * kKStageBytes + c * kKChunkBytes, &tmap_k32, c * 64, tile.kh, 32 * static_cast<int>(rank), page, full);
+          }
+          if (!alive) break;
         }
         ++req;
       }
@@ -191,6 +236,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
           const int page = __ldg(bt + blk);
           alive = tc::mbar_wait(bar(V_EMPTY0 + st), ((g >> 1) & 1) ^ 1, status, 103);
           if (!alive) break;
+          FMLA_PTRACE_AT(g, 12);
           tc::mbar_arrive_expect_tx(bar(V_LAND0 + st), kVStageBytes);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -221,7 +267,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
           tc::fence_proxy_async_smem();
           __syncwarp();
         }
-        if (lane == 0) tc::mbar_arrive_cluster(lbar(V_FULL0 + st));
+        if (lane == 0) { FMLA_PTRACE_AT(g, 13); tc::mbar_arrive_cluster(lbar(V_FULL0 + st)); }
       }
     }
   } else if (warp == 5) {
@@ -246,19 +292,19 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         if (nblk == 0) continue;
         alive = __all_sync(0xffffffffu, tc::mbar_wait_cluster(bar(Q_FULL), req & 1, status, 105));
         // One poll reads every barrier of interest, one per lane:
-        //   lane 0 P_FULL(jp)  lane 1 O_EMPTY  lane 2 V_FULL(jp)  lane 3 S_EMPTY(js)  lane 4 K_FULL(js)
-        int js = 0, jp = 0, idle = 0;
+        //   lane 0 P_FULL(jp)  lane 1 O_EMPTY  lane 2 V_FULL(jp)  lane 3 S_EMPTY(js)  lane 4 K_FULL(js, group sg)
+        int js = 0, sg = 0, jp = 0, idle = 0;
         while (jp < nblk && alive) {
           const int gs = g + min(js, nblk - 1), sts = gs & 1;
           const uint32_t phs = (gs >> 1) & 1;
           const int gp = g + jp, stp = gp & 1;
           const uint32_t php = (gp >> 1) & 1;
-          int pb = P_FULL;
-          uint32_t pp = gp & 1;
+          int pb = P_FULL0 + stp;
+          uint32_t pp = php;
           if (lane == 1) { pb = O_EMPTY; pp = (req & 1) ^ 1; }
           if (lane == 2) { pb = V_FULL0 + stp; pp = php; }
           if (lane == 3) { pb = S_EMPTY0 + sts; pp = phs ^ 1; }
-          if (lane >= 4) { pb = K_FULL0 + sts; pp = phs; }
+          if (lane >= 4) { pb = K_FULL0 + sts * kKGroups + sg; pp = phs; }
           const bool hit = lane < 5 && tc::mbar_test_wait_cluster(bar(pb), pp);
           const uint32_t m = __ballot_sync(0xffffffffu, hit);
           bool did = false;
@@ -269,25 +315,38 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
               if (stp == 0) pv_block_pair<0>(tmem, desc_p, desc_v, idesc_o, jp == 0);
               else pv_block_pair<1>(tmem, desc_p, desc_v, idesc_o, jp == 0);
               commit_both(V_EMPTY0 + stp);
-              commit_both(P_EMPTY);
+              commit_both(P_EMPTY0 + stp);
               FMLA_PTRACE_AT(gp, 5);
             }
             __syncwarp();
             ++jp;
             did = true;
-          } else if (js < nblk && (m & 0x18u) == 0x18u) {
+          } else if (js < nblk && (m & 0x10u) && (sg > 0 || (m & 0x8u))) {
             tc::tc_fence_after();
-            if (lane == 0) FMLA_PTRACE_AT(gs, 2);
+            if (lane == 0 && sg == 0) FMLA_PTRACE_AT(gs, 2);
             if (tc::elect_one()) {
-              if (sts == 0) s_block_pair<0>(tmem, desc_q, desc_k, idesc_s);
-              else s_block_pair<1>(tmem, desc_q, desc_k, idesc_s);
-              commit_both(S_FULL0 + sts);
-              commit_both(K_EMPTY0 + sts);
-              FMLA_PTRACE_AT(gs, 3);
-              if (js == nblk - 1) commit_both(Q_EMPTY);
+              if constexpr (kKGroups == 1) {
+                if (sts == 0) s_group_pair<0, 0>(tmem, desc_q, desc_k, idesc_s);
+                else s_group_pair<1, 0>(tmem, desc_q, desc_k, idesc_s);
+              } else {
+                switch (sts * kKGroups + sg) {
+                  case 0: s_group_pair<0, 0>(tmem, desc_q, desc_k, idesc_s); break;
+                  case 1: s_group_pair<0, 1>(tmem, desc_q, desc_k, idesc_s); break;
+                  case 2: s_group_pair<0, kKGroups - 1>(tmem, desc_q, desc_k, idesc_s); break;
+                  case 3: s_group_pair<1, 0>(tmem, desc_q, desc_k, idesc_s); break;
+                  case 4: s_group_pair<1, 1>(tmem, desc_q, desc_k, idesc_s); break;
+                  default: s_group_pair<1, kKGroups - 1>(tmem, desc_q, desc_k, idesc_s); break;
+                }
+              }
+              commit_both(K_EMPTY0 + sts * kKGroups + sg);
+              if (sg == kKGroups - 1) {
+                commit_both(S_FULL0 + sts);
+                FMLA_PTRACE_AT(gs, 3);
+                if (js == nblk - 1) commit_both(Q_EMPTY);
+              }
             }
             __syncwarp();
-            ++js;
+            if (++sg == kKGroups) { sg = 0; ++js; }
             did = true;
           }
           if (did) {
@@ -309,7 +368,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     // ================================ softmax / epilogue ================================
     const int r_row = tid & 63, th = tid >> 6;           // TMEM lane tid: row tid%64, token/column half tid/64
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t l_s_empty0 = lbar(S_EMPTY0), l_p_full = lbar(P_FULL), l_o_empty = lbar(O_EMPTY);
+    const uint32_t l_s_empty0 = lbar(S_EMPTY0), l_p_full0 = lbar(P_FULL0), l_o_empty = lbar(O_EMPTY);
     int g = 0, req = 0;
     bool aborted = false;        // uniform over the 128 softmax threads: only read right after a bar_sync
     for (int wi = 0; wi < tile.n_work; ++wi) {
@@ -351,6 +410,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         xch[tid] = mx;
         bar_sync(1, 128);
         if (*sAbort) { aborted = true; break; }
+        if (tid == 0) FMLA_PTRACE_AT(g, 8);
         mx = fmaxf(mx, xch[tid ^ 64]);
         const float m_new = fmaxf(m_run, mx);
 
@@ -362,10 +422,10 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         }
         m_run = m_new;
         const bool any_need = __any_sync(0xffffffffu, need);
-        bool pv_done = false;    // the previous P V must be complete before O is rescaled and before P is overwritten
+        // P has two buffers (block g uses buffer g & 1): writing it needs P V of block g-2 to be complete;
+        // rescaling O needs every earlier P V to be complete, i.e. that of block g-1 (they complete in order)
         if (any_need) {
-          if (!tc::mbar_wait(bar(P_EMPTY), (g & 1) ^ 1, status, 109)) *sAbort = 1;
-          pv_done = true;
+          if (j > 0 && !tc::mbar_wait(bar(P_EMPTY0 + ((g - 1) & 1)), ((g - 1) >> 1) & 1, status, 109)) *sAbort = 1;
           const float m_next = need ? m_new : m_used;
           const float alpha = exp2f(m_used - m_next);
           m_used = m_next;
@@ -393,20 +453,21 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
           pk[i] = pack_16x2<F16>(p0, p1);
         }
         l_part += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-        if (!pv_done && !tc::mbar_wait(bar(P_EMPTY), (g & 1) ^ 1, status, 109)) *sAbort = 1;
+        if (!tc::mbar_wait(bar(P_EMPTY0 + st), ((g >> 1) & 1) ^ 1, status, 109)) *sAbort = 1;
         if (tid == 0) FMLA_PTRACE_AT(g, 9);
         // P[row][th*32 .. +32) -> K-major 128B-swizzled A operand: 16-byte chunk (th*4 + q) ^ (row & 7)
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4)
-          pst_shared_v4(sP + r_row * 128 + ((((th * 4 + q4) ^ (r_row & 7))) << 4),
+          pst_shared_v4(sP + st * kChunkBytes + r_row * 128 + ((((th * 4 + q4) ^ (r_row & 7))) << 4),
                         make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]));
         tc::fence_proxy_async_smem();
-        tc::mbar_arrive_cluster(l_p_full);
+        tc::mbar_arrive_cluster(l_p_full0 + st * 8);
         if (tid == 0) FMLA_PTRACE_AT(g, 11);
       }
 
       // ---- epilogue of this work item ---------------------------------------------------
       float* xch = sMx + 256;
+      if (tid == 0) FMLA_PTRACE_AT(g - 1, 14);
       bar_sync(1, 128);
       xch[tid] = l_part;
       bar_sync(1, 128);
@@ -460,6 +521,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         tc::mbar_arrive_cluster(l_o_empty);
         ++req;
       }
+      if (tid == 0) FMLA_PTRACE_AT(g - 1, 15);
       if (th == 0) {
         if (r.no_split) {
           p.softmax_lse[((int64_t)r.batch * p.h_q + head) * p.s_q + tile.sq] = inv == 0.f ? pos_inf() : (log2f(l) + m_used) * kLn2;
@@ -475,6 +537,13 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
   __syncthreads();
   tc::cluster_sync_all();
   if (warp == 5) tc::tmem_dealloc_pair(tmem, 512);
+#ifdef FMLA_TRACE
+  if (tid == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_pair_span[(blockIdx.z * gridDim.x + blockIdx.x) * 2 + 1] = (long long)t;
+  }
+#endif
 }
 
 // ---- host side ----------------------------------------------------------------------------------
@@ -510,6 +579,11 @@ bool decode_dense_pair_applies(const DecodeKernelParams& p) { return p.hq_per_hk
 cudaError_t launch_decode_dense_pair(const DecodeKernelParams& p, cudaStream_t stream) {
   TcParams P = {};
   P.d = p;
+  static const int prefetch = [] {
+    const char* v = getenv("FMLA_PAIR_PREFETCH");
+    return v ? atoi(v) : 0;
+  }();
+  P.d.l2_prefetch_dist = prefetch;
   CUtensorMap tq, tk, tv;
   // q [b][s_q][h_q][576] ; box = 64 heads x 64 columns
   if (!pair_map_4d(&tq, p.q, p.h_q, p.s_q, p.b, p.q_stride_h, p.q_stride_s, p.q_stride_b, 64, 1)) return cudaErrorInvalidValue;
@@ -542,6 +616,9 @@ cudaError_t launch_decode_dense_pair(const DecodeKernelParams& p, cudaStream_t s
 #ifdef FMLA_TRACE
 extern "C" int fmla_debug_read_pair_trace(long long* host, int n) {
   return (int)cudaMemcpyFromSymbol(host, g_pair_trace, sizeof(long long) * n);
+}
+extern "C" int fmla_debug_read_pair_span(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_pair_span, sizeof(long long) * n);
 }
 #endif
 

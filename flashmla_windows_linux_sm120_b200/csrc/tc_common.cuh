@@ -192,18 +192,21 @@ __device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
-// arrivals on a barrier that may live in the other CTA of the cluster
+// Arrivals on a barrier that may live in the other CTA of the cluster.  What these arrivals order is work of
+// the async proxy and of the tensor pipe (made visible by fence.proxy.async / tcgen05.fence before the arrive),
+// not generic-proxy memory traffic between the CTAs, so the default semantics are used: a release at cluster
+// scope in front of every arrive cost the softmax threads several hundred clocks per 64-token block.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_bar) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_bar) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;\n" ::"r"(cluster_bar), "r"(bytes) : "memory");
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;\n" ::"r"(cluster_bar), "r"(bytes) : "memory");
 }
-// wait on a barrier of this CTA whose arrivals come from both CTAs (acquire at cluster scope)
+// wait on a barrier of this CTA whose arrivals come from both CTAs
 __device__ __forceinline__ bool mbar_test_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-      "{\n.reg .pred p;\nmbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
@@ -212,7 +215,7 @@ __device__ __forceinline__ bool mbar_test_wait_cluster(uint32_t bar, uint32_t pa
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-      "{\n.reg .pred p;\nmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
