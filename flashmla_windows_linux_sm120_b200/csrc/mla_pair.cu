@@ -9,19 +9,29 @@
 //               stages 64 tokens x 256 value columns (32 KB): chunks {2r, 2r+1, 4+2r, 5+2r} of the page
 // What this buys over one CTA per 64 heads with a 72 KB page stage that is held from its load until the end
 // of its P V: the K part is released right after S and the V part is loaded independently of it, so two
-// small rings (2 x 36 KB + 2 x 32 KB) keep more loads in flight per SM than two 72 KB stages, and the paired
+// small rings (3 x 36 KB + 2 x 32 KB) keep more loads in flight per SM than two 72 KB stages, and the paired
 // instructions run at 25 / 65 clocks (S / P V) instead of 32 / 81.
+// Two thirds of Q live in tensor memory: the 192 columns that O and S leave idle hold column chunks 0..5 of
+// the CTA's Q tile (tcgen05.cp from shared memory, rows duplicated into both lane halves as an M=64-per-CTA
+// A operand wants them), so only chunks 6..8 (24 KB) stay in shared memory -- that is what makes room for
+// the third K stage -- and the S instructions that take A from tensor memory run at 18 instead of 25 clocks.
+// The six chunks pass through the (then idle) K ring on their way: a request's K loads start once its Q copy
+// into tensor memory has completed.
 //
 //   warps 0-3 softmax : as in mla_tc.cu (TMEM lane = row + 64 * (token >= 32)); arrivals that the issuing
 //                       thread waits for go to the leader's barriers (remote arrive from rank 1)
-//   warp 4   K loader : Q tile, then per 64-token block the CTA's 32 token rows; the copies complete on the
-//                       LEADER's barrier (cp.async.bulk.tensor ... cta_group::2, no multicast)
-//   warp 5   MMA      : rank 0 only
+//   warp 4   K loader : Q tile, then per 64-token block the CTA's 32 token rows.  The leader's copies complete on
+//                       the barrier its MMA warp waits on; the peer's copies complete on a barrier of the peer
+//                       and one thread there passes each completion on with a single remote arrive (letting the
+//                       peer's copies count their bytes on the leader's barrier directly -- cp.async.bulk.tensor
+//                       ... cta_group::2 -- made a 36 KB part take about 3 us to be seen as landed)
+//   warp 5   MMA      : rank 0: issues every MMA; rank 1: the relay of the Q / K completions just described
 //   warp 6   V loader : per block 4 boxes of 64 rows x 64 columns, completing on a local barrier
 //   warp 7   V relay  : waits for the local V part, clears the rows of the last page that lie beyond the
 //                       sequence (they may hold NaN and 0 * NaN must not reach O), tells the leader
-// TMEM (512 columns per CTA, allocated as a pair): O = [0,256), S[0] = [256,288), S[1] = [288,320); layouts as
-// in mla_tc.cu (the 64-row halves of an M=128 pair instruction have the layout of the M=64 .ws form).
+// TMEM (512 columns per CTA, allocated as a pair): O = [0,256), S[0] = [256,288), S[1] = [288,320), Q chunks
+// 0..5 = [320,512) (32 columns each); O / S layouts as in mla_tc.cu (the 64-row halves of an M=128 pair
+// instruction have the layout of the M=64 .ws form).
 //
 // Semantics follow csrc/sm90/decode/dense/splitkv_mla.cu:948-957, 1022-1042, 1237-1269 of the reference
 // (borders, split outputs, LSE conventions).  Every wait is bounded; on expiry the pair drains and frees
@@ -39,33 +49,27 @@ namespace fmla {
 namespace ptc {
 constexpr int kChunkBytes = 64 * 128;             // Q / P / V chunk: [64 rows x 64 x 16-bit], 128-byte rows
 constexpr int kQBytes = 9 * kChunkBytes;          // 64 heads x 576
+constexpr int kQTmemChunks = 6;                   // column chunks 0..5 of Q are kept in tensor memory
+constexpr int kQSmemChunks = 9 - kQTmemChunks;    // chunks 6..8 stay in shared memory
 constexpr int kKChunkBytes = 32 * 128;            // K chunk of this CTA: [32 token rows x 64 columns]
 constexpr int kKStageBytes = 9 * kKChunkBytes;    // 36 864
+constexpr int kKStages = 3;
 constexpr int kVStageBytes = 4 * kChunkBytes;     // 32 768: 64 tokens x 256 value columns
-constexpr int Q_OFF = 0;
-constexpr int K_OFF = Q_OFF + kQBytes;            // 2 stages
-constexpr int V_OFF = K_OFF + 2 * kKStageBytes;   // 2 stages
+constexpr int Q_OFF = 0;                          // kQSmemChunks chunks
+constexpr int K_OFF = Q_OFF + kQSmemChunks * kChunkBytes;   // kKStages stages; also the staging area of Q chunks 0..5
+constexpr int V_OFF = K_OFF + kKStages * kKStageBytes;      // 2 stages
 constexpr int P_OFF = V_OFF + 2 * kVStageBytes;   // 2 x [64 x 64]
 constexpr int BAR_OFF = P_OFF + 2 * kChunkBytes;
 constexpr int MX_OFF = BAR_OFF + 256;             // float [3][128] exchange
 constexpr int MISC_OFF = MX_OFF + 1536;
 constexpr int SMEM_BYTES = MISC_OFF + 64;
+static_assert(kQTmemChunks * kChunkBytes <= kKStages * kKStageBytes, "Q staging must fit into the K ring");
 // leader-side barriers (waited on by the MMA warp of rank 0; arrivals come from both CTAs)
 // and per-CTA barriers (each CTA waits on its own copy; the leader's commits arrive on both copies)
-// The K part of a block can be handled in kKGroups groups of column chunks, each with its own full / empty
-// barrier (a group is refilled as soon as the S instructions that read it have completed).  Measured on the
-// benchmark shape: 3 groups stretch S over the arrival of its last group and nearly double the step
-// (3150 instead of 1810 clocks per block), so one group is used.
-#ifndef FMLA_PAIR_KGROUPS
-#define FMLA_PAIR_KGROUPS 1
-#endif
-constexpr int kKGroups = FMLA_PAIR_KGROUPS;
-constexpr int kChunksPerGroup = 9 / kKGroups;
-static_assert(kKGroups == 1 || kKGroups == 3, "9 column chunks split into 1 or 3 groups");
-enum Bar { Q_FULL = 0, K_FULL0, K_FULL_END = K_FULL0 + 2 * kKGroups - 1, V_FULL0, V_FULL1, S_EMPTY0, S_EMPTY1, P_FULL0, P_FULL1, O_EMPTY,
-           Q_EMPTY, K_EMPTY0, K_EMPTY_END = K_EMPTY0 + 2 * kKGroups - 1, V_EMPTY0, V_EMPTY1, V_LAND0, V_LAND1, S_FULL0, S_FULL1,
-           P_EMPTY0, P_EMPTY1, O_FULL, NUM_BARS };
-constexpr int TMEM_O = 0, TMEM_S = 256;
+enum Bar { Q_FULL = 0, K_FULL0, K_FULL1, K_FULL2, V_FULL0, V_FULL1, S_EMPTY0, S_EMPTY1, P_FULL0, P_FULL1, O_EMPTY,
+           Q_EMPTY, QT_DONE, K_EMPTY0, K_EMPTY1, K_EMPTY2, V_EMPTY0, V_EMPTY1, V_LAND0, V_LAND1, S_FULL0, S_FULL1,
+           P_EMPTY0, P_EMPTY1, O_FULL, Q_LAND, K_LAND0, K_LAND1, K_LAND2, NUM_BARS };
+constexpr int TMEM_O = 0, TMEM_S = 256, TMEM_Q = 320;
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory limit per CTA");
 static_assert(NUM_BARS * 8 <= 256, "barrier area too small");
 constexpr float kRescaleThreshold = 8.0f;
@@ -84,35 +88,58 @@ __device__ long long g_pair_span[512 * 2];       // per CTA: first and last cloc
 #ifndef FMLA_TRACE_PART
 #define FMLA_TRACE_PART 0
 #endif
+// cross-CTA timeline in nanoseconds (globaltimer): [block][rank][slot]
+__device__ long long g_pair_gt[160 * 2 * 8];
+__device__ long long g_pair_head[256][2];
+__device__ __forceinline__ long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return (long long)t; }
+#define FMLA_GTRACE_AT(blk, rk, slot)                                                       \
+  do {                                                                                       \
+    if (blockIdx.y == 0 && blockIdx.z == FMLA_TRACE_PART && blockIdx.x < 2 && (blk) < 160) g_pair_gt[((blk) * 2 + (rk)) * 8 + (slot)] = gtime(); \
+  } while (0)
 #else
 #define FMLA_PTRACE_AT(blk, slot) do {} while (0)
+#define FMLA_GTRACE_AT(blk, rk, slot) do {} while (0)
 #endif
 
 __device__ __forceinline__ void pst_shared_v4(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// The S instructions of column-chunk group GRP of one block in stage ST: descriptors are a warp-uniform base
-// plus an immediate.
-template <int ST, int GRP>
-__device__ __forceinline__ void s_group_pair(uint32_t tmem, uint64_t desc_q, uint64_t desc_k, uint32_t idesc) {
+__device__ __forceinline__ void mma_pair_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// shared memory -> tensor memory, 64 rows x 16 bytes per instruction, rows 0..31 into lanes 0..31 and 64..95,
+// rows 32..63 into lanes 32..63 and 96..127, in both CTAs of the pair (each from its own shared memory)
+__device__ __forceinline__ void tmem_cp_pair_64x128b(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::2.64x128b.warpx2::02_13 [%0], %1;\n" ::"r"(taddr), "l"(desc) : "memory");
+}
+
+// The 36 S instructions of one block: descriptors and tensor memory addresses are a warp-uniform base (which
+// carries the ring stage, chosen at run time) plus an immediate.  One copy of this code serves every stage:
+// with one unrolled copy per (K stage, S buffer) the issuing thread ran out of instruction cache -- each copy
+// came around once in six blocks and cost about 300 ns of instruction fetch before its first MMA.
+__device__ __forceinline__ void s_block_pair(uint32_t tmem_s, uint32_t tmem_q, uint64_t desc_q, uint64_t desc_k_stage, uint32_t idesc) {
   using namespace ptc;
 #pragma unroll
-  for (int c = kChunksPerGroup * GRP; c < kChunksPerGroup * (GRP + 1); ++c)
+  for (int c = 0; c < 9; ++c)
 #pragma unroll
-    for (int s = 0; s < 4; ++s)
-      tc::mma_pair_ss(tmem + TMEM_S + ST * 32, tc::desc_advance(desc_q, c * kChunkBytes + s * 32),
-                      tc::desc_advance(desc_k, ST * kKStageBytes + c * kKChunkBytes + s * 32), idesc, (c | s) ? 1u : 0u);
+    for (int s = 0; s < 4; ++s) {
+      const uint64_t db = tc::desc_advance(desc_k_stage, c * kKChunkBytes + s * 32);
+      if (c < kQTmemChunks) mma_pair_ts(tmem_s, tmem_q + c * 32 + s * 8, db, idesc, (c | s) ? 1u : 0u);
+      else tc::mma_pair_ss(tmem_s, tc::desc_advance(desc_q, (c - kQTmemChunks) * kChunkBytes + s * 32), db, idesc, 1u);
+    }
 }
-template <int ST>
-__device__ __forceinline__ void pv_block_pair(uint32_t tmem, uint64_t desc_p, uint64_t desc_v, uint32_t idesc, bool first) {
+__device__ __forceinline__ void pv_block_pair(uint32_t tmem_o, uint64_t desc_p_stage, uint64_t desc_v_stage, uint32_t idesc, bool first) {
   using namespace ptc;
 #pragma unroll
   for (int h = 0; h < 2; ++h)
 #pragma unroll
     for (int s = 0; s < 4; ++s)
-      tc::mma_pair_ss(tmem + TMEM_O + h * 128, tc::desc_advance(desc_p, ST * kChunkBytes + s * 32),
-                      tc::desc_advance(desc_v, ST * kVStageBytes + h * 2 * kChunkBytes + s * 2048), idesc, (first && s == 0) ? 0u : 1u);
+      tc::mma_pair_ss(tmem_o + h * 128, tc::desc_advance(desc_p_stage, s * 32),
+                      tc::desc_advance(desc_v_stage, h * 2 * kChunkBytes + s * 2048), idesc, (first && s == 0) ? 0u : 1u);
 }
 
 // grid (s_q * hq_per_hk / 64, h_k, parts), clusters of two CTAs along x; 256 threads
@@ -148,7 +175,9 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
 
   if (tid == 0) {
     tc::mbar_init(bar(Q_FULL), 2);
-    for (int i = K_FULL0; i <= K_FULL_END; ++i) tc::mbar_init(bar(i), 2);
+    tc::mbar_init(bar(K_FULL0), 2);
+    tc::mbar_init(bar(K_FULL1), 2);
+    tc::mbar_init(bar(K_FULL2), 2);
     tc::mbar_init(bar(V_FULL0), 2);
     tc::mbar_init(bar(V_FULL1), 2);
     tc::mbar_init(bar(S_EMPTY0), 256);
@@ -182,9 +211,17 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         if (r.blk_hi == r.blk_lo) continue;
         alive = tc::mbar_wait(bar(Q_EMPTY), (req & 1) ^ 1, status, 101);
         if (!alive) break;
-        tc::mbar_arrive_expect_tx_cluster(lbar(Q_FULL), kQBytes);
+        // every S of the previous request has completed: its Q (shared and tensor memory) and the whole K ring
+        // are free.  Chunks 0..5 of the new Q are staged at the start of the K ring, chunks 6..8 go to their place.
+        const uint32_t q_bar = rank == 0 ? bar(Q_FULL) : bar(Q_LAND);
+        tc::mbar_arrive_expect_tx(q_bar, kQBytes);
 #pragma unroll
-        for (int c = 0; c < 9; ++c) tc::tma_load_4d_pair(sQ + c * kChunkBytes, &tmap_q, c * 64, tile.head0, tile.sq, r.batch, lbar(Q_FULL));
+        for (int c = 0; c < 9; ++c)
+          tc::tma_load_4d(c < kQTmemChunks ? sK + c * kChunkBytes : sQ + (c - kQTmemChunks) * kChunkBytes, &tmap_q, c * 64, tile.head0,
+                          tile.sq, r.batch, q_bar);
+        // the K ring may be refilled once the leader has copied the staged chunks into tensor memory
+        alive = tc::mbar_wait(bar(QT_DONE), req & 1, status, 107);
+        if (!alive) break;
         const int* bt = p.block_table + r.batch * p.block_table_stride_b;
         const int pf = p.l2_prefetch_dist;
         // the leader pulls whole pages into L2 `pf` blocks ahead of the loads of both CTAs (the V parts use the
@@ -198,7 +235,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         }
         int page_next = __ldg(bt + r.blk_lo);
         for (int blk = r.blk_lo; blk < r.blk_hi; ++blk, ++g) {
-          const int st = g & 1;
+          const int st = g % kKStages;
           const int page = page_next;
           if (blk + 1 < r.blk_hi) page_next = __ldg(bt + blk + 1);
           if (pf > 0 && rank == 0 && blk + pf < r.blk_hi) {
@@ -206,18 +243,15 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
 #pragma unroll
             for (int c = 0; c < 9; ++c) tc::tma_prefetch_l2_4d(&tmap_v64, c * 64, tile.kh, 0, pg);
           }
-#pragma unroll
-          for (int grp = 0; grp < kKGroups; ++grp) {
-            alive = alive && tc::mbar_wait(bar(K_EMPTY0 + st * kKGroups + grp), ((g >> 1) & 1) ^ 1, status, 102);
-            if (!alive) break;
-            if (grp == 0) FMLA_PTRACE_AT(g, 0);
-            const uint32_t full = lbar(K_FULL0 + st * kKGroups + grp);
-            tc::mbar_arrive_expect_tx_cluster(full, kChunksPerGroup * kKChunkBytes);
-#pragma unroll
-            for (int c = kChunksPerGroup * grp; c < kChunksPerGroup * (grp + 1); ++c)
-              tc::tma_load_4d_pair(sK + st * kKStageBytes + c * kKChunkBytes, &tmap_k32, c * 64, tile.kh, 32 * static_cast<int>(rank), page, full);
-          }
+          alive = tc::mbar_wait(bar(K_EMPTY0 + st), ((g / kKStages) & 1) ^ 1, status, 102);
           if (!alive) break;
+          FMLA_PTRACE_AT(g, 0);
+          FMLA_GTRACE_AT(g, rank, 7);
+          const uint32_t full = rank == 0 ? bar(K_FULL0 + st) : bar(K_LAND0 + st);
+          tc::mbar_arrive_expect_tx(full, kKStageBytes);
+#pragma unroll
+          for (int c = 0; c < 9; ++c)
+            tc::tma_load_4d(sK + st * kKStageBytes + c * kKChunkBytes, &tmap_k32, c * 64, tile.kh, 32 * static_cast<int>(rank), page, full);
         }
         ++req;
       }
@@ -237,12 +271,17 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
           alive = tc::mbar_wait(bar(V_EMPTY0 + st), ((g >> 1) & 1) ^ 1, status, 103);
           if (!alive) break;
           FMLA_PTRACE_AT(g, 12);
+#ifdef FMLA_EXP_NO_V_LOAD      // timing experiment only: results are wrong
+          tc::mbar_arrive(bar(V_LAND0 + st));
+          (void)page;
+#else
           tc::mbar_arrive_expect_tx(bar(V_LAND0 + st), kVStageBytes);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int chunk = (i >> 1) * 4 + 2 * static_cast<int>(rank) + (i & 1);     // value columns 64*chunk ..
             tc::tma_load_4d(sV + st * kVStageBytes + i * kChunkBytes, &tmap_v64, chunk * 64, tile.kh, 0, page, bar(V_LAND0 + st));
           }
+#endif
         }
       }
     }
@@ -270,12 +309,30 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         if (lane == 0) { FMLA_PTRACE_AT(g, 13); tc::mbar_arrive_cluster(lbar(V_FULL0 + st)); }
       }
     }
+  } else if (warp == 5 && rank != 0) {
+    // ================================ Q / K relay (peer only) ==========================
+    int g = 0, req = 0;
+    bool alive = true;
+    for (int wi = 0; wi < tile.n_work && alive; ++wi) {
+      const Work r = get_work<kDense>(P, tile, wi);
+      if (r.blk_hi == r.blk_lo) continue;
+      alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_LAND), req & 1, status, 111));
+      if (!alive) break;
+      if (lane == 0) tc::mbar_arrive_cluster(lbar(Q_FULL));
+      for (int blk = r.blk_lo; blk < r.blk_hi && alive; ++blk, ++g) {
+        const int st = g % kKStages;
+        alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(K_LAND0 + st), (g / kKStages) & 1, status, 112));
+        if (alive && lane == 0) tc::mbar_arrive_cluster(lbar(K_FULL0 + st));
+      }
+      ++req;
+    }
   } else if (warp == 5) {
     // ================================ MMA issuer (leader only) =========================
     if (rank == 0) {
       constexpr uint32_t idesc_s = tc::idesc_bf16_f32(128, 64, 0, 0, F16);
       constexpr uint32_t idesc_o = tc::idesc_bf16_f32(128, 256, 0, 1, F16);
-      const uint64_t desc_q = tc::smem_desc_sw128(sQ, 16, 1024);             // A of S: K-major
+      const uint64_t desc_q = tc::smem_desc_sw128(sQ, 16, 1024);             // A of S, chunks 6..8: K-major
+      const uint64_t desc_qstage = tc::smem_desc_sw128(sK, 16, 1024);        // chunks 0..5 of Q where the loader stages them
       const uint64_t desc_k = tc::smem_desc_sw128(sK, 16, 1024);             // B of S: K-major, 32 rows per CTA (stage 0)
       const uint64_t desc_p = tc::smem_desc_sw128(sP, 16, 1024);             // A of PV: K-major
       const uint64_t desc_v = tc::smem_desc_sw128(sV, kChunkBytes, 1024);    // B of PV: MN-major, 64-wide column groups 8 KB apart
@@ -286,77 +343,102 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
       };
       int g = 0, req = 0;
       bool alive = true;
+#ifdef FMLA_TRACE
+      int seen_k = -1, seen_s = -1, seen_p = -1, seen_v = -1, after_issue = 0;
+#endif
       for (int wi = 0; wi < tile.n_work && alive; ++wi) {
         const Work r = get_work<kDense>(P, tile, wi);
         const int nblk = r.blk_hi - r.blk_lo;
         if (nblk == 0) continue;
         alive = __all_sync(0xffffffffu, tc::mbar_wait_cluster(bar(Q_FULL), req & 1, status, 105));
+        if (!alive) break;
+        // Q chunks 0..5: shared memory -> tensor memory of both CTAs (8 copies of 64 rows x 16 bytes per chunk)
+        tc::tc_fence_after();
+        if (tc::elect_one()) {
+#pragma unroll
+          for (int c = 0; c < kQTmemChunks; ++c)
+#pragma unroll
+            for (int sub = 0; sub < 8; ++sub)
+              tmem_cp_pair_64x128b(tmem + TMEM_Q + c * 32 + sub * 4, tc::desc_advance(desc_qstage, c * kChunkBytes + sub * 16));
+          commit_both(QT_DONE);
+        }
+        __syncwarp();
         // One poll reads every barrier of interest, one per lane:
-        //   lane 0 P_FULL(jp)  lane 1 O_EMPTY  lane 2 V_FULL(jp)  lane 3 S_EMPTY(js)  lane 4 K_FULL(js, group sg)
-        int js = 0, sg = 0, jp = 0, idle = 0;
+        //   lane 0 P_FULL(jp)  lane 1 O_EMPTY  lane 2 V_FULL(jp)  lane 3 S_EMPTY(js)  lane 4 K_FULL(js)
+        int js = 0, jp = 0, idle = 0;
         while (jp < nblk && alive) {
-          const int gs = g + min(js, nblk - 1), sts = gs & 1;
-          const uint32_t phs = (gs >> 1) & 1;
+#ifdef FMLA_TRACE
+          if (lane == 0 && after_issue && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == FMLA_TRACE_PART) {   // first pass through the loop head after an issue: rank-0 slots 1 / 10 hold ns
+            if (after_issue == 1) g_pair_head[(g + js - 1) & 255][0] = gtime(); else g_pair_head[(g + jp - 1) & 255][1] = gtime();
+          }
+          after_issue = 0;
+#endif
+          const int gs = g + min(js, nblk - 1), sbs = gs & 1, kst = gs % kKStages;
+          const uint32_t phs = (gs >> 1) & 1, phk = (gs / kKStages) & 1;
           const int gp = g + jp, stp = gp & 1;
           const uint32_t php = (gp >> 1) & 1;
           int pb = P_FULL0 + stp;
           uint32_t pp = php;
           if (lane == 1) { pb = O_EMPTY; pp = (req & 1) ^ 1; }
           if (lane == 2) { pb = V_FULL0 + stp; pp = php; }
-          if (lane == 3) { pb = S_EMPTY0 + sts; pp = phs ^ 1; }
-          if (lane >= 4) { pb = K_FULL0 + sts * kKGroups + sg; pp = phs; }
+          if (lane == 3) { pb = S_EMPTY0 + sbs; pp = phs ^ 1; }
+          if (lane >= 4) { pb = K_FULL0 + kst; pp = phk; }
           const bool hit = lane < 5 && tc::mbar_test_wait_cluster(bar(pb), pp);
           const uint32_t m = __ballot_sync(0xffffffffu, hit);
+#ifdef FMLA_TRACE
+          if (lane == 0) {     // first time each input of the next S / P V is seen ready (rank-1 slots 3..6 of the timeline)
+            if ((m & 0x10u) && js < nblk && seen_k != gs) { seen_k = gs; FMLA_GTRACE_AT(gs, 1, 3); }
+            if ((m & 0x8u) && js < nblk && seen_s != gs) { seen_s = gs; FMLA_GTRACE_AT(gs, 1, 4); }
+            if ((m & 0x1u) && jp < js && seen_p != gp) { seen_p = gp; FMLA_GTRACE_AT(gp, 1, 5); }
+            if ((m & 0x4u) && jp < js && seen_v != gp) { seen_v = gp; FMLA_GTRACE_AT(gp, 1, 6); }
+          }
+#endif
           bool did = false;
           if (jp < js && (m & 5u) == 5u && (jp > 0 || (m & 2u))) {
             tc::tc_fence_after();
-            if (lane == 0) FMLA_PTRACE_AT(gp, 4);
+            if (lane == 0) { FMLA_PTRACE_AT(gp, 4); FMLA_GTRACE_AT(gp, 0, 5); }
             if (tc::elect_one()) {
-              if (stp == 0) pv_block_pair<0>(tmem, desc_p, desc_v, idesc_o, jp == 0);
-              else pv_block_pair<1>(tmem, desc_p, desc_v, idesc_o, jp == 0);
+#ifndef FMLA_EXP_NO_PV         // timing experiment only: results are wrong
+              pv_block_pair(tmem + TMEM_O, tc::desc_advance(desc_p, stp * kChunkBytes), tc::desc_advance(desc_v, stp * kVStageBytes), idesc_o, jp == 0);
+#endif
               commit_both(V_EMPTY0 + stp);
               commit_both(P_EMPTY0 + stp);
               FMLA_PTRACE_AT(gp, 5);
+              FMLA_GTRACE_AT(gp, 0, 6);
             }
             __syncwarp();
             ++jp;
             did = true;
-          } else if (js < nblk && (m & 0x10u) && (sg > 0 || (m & 0x8u))) {
+#ifdef FMLA_TRACE
+            after_issue = 2;
+#endif
+          } else if (js < nblk && (m & 0x18u) == 0x18u) {
             tc::tc_fence_after();
-            if (lane == 0 && sg == 0) FMLA_PTRACE_AT(gs, 2);
+            if (lane == 0) { FMLA_PTRACE_AT(gs, 2); FMLA_GTRACE_AT(gs, 0, 3); }
             if (tc::elect_one()) {
-              if constexpr (kKGroups == 1) {
-                if (sts == 0) s_group_pair<0, 0>(tmem, desc_q, desc_k, idesc_s);
-                else s_group_pair<1, 0>(tmem, desc_q, desc_k, idesc_s);
-              } else {
-                switch (sts * kKGroups + sg) {
-                  case 0: s_group_pair<0, 0>(tmem, desc_q, desc_k, idesc_s); break;
-                  case 1: s_group_pair<0, 1>(tmem, desc_q, desc_k, idesc_s); break;
-                  case 2: s_group_pair<0, kKGroups - 1>(tmem, desc_q, desc_k, idesc_s); break;
-                  case 3: s_group_pair<1, 0>(tmem, desc_q, desc_k, idesc_s); break;
-                  case 4: s_group_pair<1, 1>(tmem, desc_q, desc_k, idesc_s); break;
-                  default: s_group_pair<1, kKGroups - 1>(tmem, desc_q, desc_k, idesc_s); break;
-                }
-              }
-              commit_both(K_EMPTY0 + sts * kKGroups + sg);
-              if (sg == kKGroups - 1) {
-                commit_both(S_FULL0 + sts);
-                FMLA_PTRACE_AT(gs, 3);
-                if (js == nblk - 1) commit_both(Q_EMPTY);
-              }
+              s_block_pair(tmem + TMEM_S + sbs * 32, tmem + TMEM_Q, desc_q, tc::desc_advance(desc_k, kst * kKStageBytes), idesc_s);
+              commit_both(S_FULL0 + sbs);
+              commit_both(K_EMPTY0 + kst);
+              FMLA_PTRACE_AT(gs, 3);
+              FMLA_GTRACE_AT(gs, 0, 4);
+              if (js == nblk - 1) commit_both(Q_EMPTY);
             }
             __syncwarp();
-            if (++sg == kKGroups) { sg = 0; ++js; }
+            ++js;
             did = true;
+#ifdef FMLA_TRACE
+            after_issue = 1;
+#endif
           }
           if (did) {
             idle = 0;
           } else if (++idle > tc::kSpinLimit) {
             if (lane == 0) tc::report_status(status, 106);
             alive = false;
-          } else {
-            __nanosleep(20);
           }
+#ifdef FMLA_PAIR_POLL_SLEEP
+          else { __nanosleep(FMLA_PAIR_POLL_SLEEP); }
+#endif
         }
         g += nblk;
         if (alive && tc::elect_one()) commit_both(O_FULL);
@@ -382,7 +464,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         uint32_t sv[32];
         uint32_t vbits = 0xffffffffu;
         if (tc::mbar_wait(bar(S_FULL0 + st), (g >> 1) & 1, status, 108)) {
-          if (tid == 0) FMLA_PTRACE_AT(g, 6);
+          if (tid == 0) { FMLA_PTRACE_AT(g, 6); FMLA_GTRACE_AT(g, rank, 0); }
           tc::tc_fence_after();
           tc::tmem_ld32(tmem + lane_addr + TMEM_S + st * 32, sv);
           tc::tmem_wait_ld();
@@ -393,7 +475,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
           for (int i = 0; i < 32; ++i) sv[i] = 0u;
         }
         tc::mbar_arrive_cluster(l_s_empty0 + st * 8);
-        if (tid == 0) FMLA_PTRACE_AT(g, 7);
+        if (tid == 0) { FMLA_PTRACE_AT(g, 7); FMLA_GTRACE_AT(g, rank, 1); }
 
         const int tok0 = (r.blk_lo + j) * 64 + th * 32;
         if (tok0 + 32 > r.border) vbits = tok0 >= r.border ? 0u : (0xffffffffu >> (32 - (r.border - tok0)));
@@ -462,7 +544,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
                         make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]));
         tc::fence_proxy_async_smem();
         tc::mbar_arrive_cluster(l_p_full0 + st * 8);
-        if (tid == 0) FMLA_PTRACE_AT(g, 11);
+        if (tid == 0) { FMLA_PTRACE_AT(g, 11); FMLA_GTRACE_AT(g, rank, 2); }
       }
 
       // ---- epilogue of this work item ---------------------------------------------------
@@ -616,6 +698,12 @@ cudaError_t launch_decode_dense_pair(const DecodeKernelParams& p, cudaStream_t s
 #ifdef FMLA_TRACE
 extern "C" int fmla_debug_read_pair_trace(long long* host, int n) {
   return (int)cudaMemcpyFromSymbol(host, g_pair_trace, sizeof(long long) * n);
+}
+extern "C" int fmla_debug_read_pair_gt(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_pair_gt, sizeof(long long) * n);
+}
+extern "C" int fmla_debug_read_pair_head(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_pair_head, sizeof(long long) * n);
 }
 extern "C" int fmla_debug_read_pair_span(long long* host, int n) {
   return (int)cudaMemcpyFromSymbol(host, g_pair_span, sizeof(long long) * n);
