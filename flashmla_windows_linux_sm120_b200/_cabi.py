@@ -29,6 +29,7 @@ class DecodeParams(C.Structure):
         ("softmax_lse", vp), ("lse_accum", vp), ("o_accum", vp),
         ("profile_event_begin", vp), ("profile_event_end", vp),
         ("indices_logical", i32),
+        ("arrival_counters", vp),
     ]
 
 

@@ -171,7 +171,7 @@ int fmla_get_mla_metadata(const int32_t* seqlens_k, int batch, int num_sm_parts,
                           int32_t* tile_scheduler_metadata, int32_t* num_splits, void* stream) {
   FMLA_REQUIRE(seqlens_k && tile_scheduler_metadata && num_splits, "null pointer");
   FMLA_REQUIRE(batch > 0, "batch must be positive");
-  FMLA_REQUIRE(num_sm_parts > 0, "num_sm_parts must be positive");
+  FMLA_REQUIRE(num_sm_parts > 0 && num_sm_parts <= 1023, "num_sm_parts must be in 1..1023");
   FMLA_REQUIRE(topk == -1 || topk > 0, "topk must be -1 (dense) or positive");
   FMLA_REQUIRE(aligned16(tile_scheduler_metadata), "tile_scheduler_metadata must be 16-byte aligned");
   cudaError_t e = fmla::launch_get_mla_metadata(seqlens_k, batch, num_sm_parts, topk, tile_scheduler_metadata, num_splits,
@@ -239,6 +239,7 @@ static int decode_impl(const fmla_decode_params* P, const fmla_peer_push* push, 
   k.tile_scheduler_metadata = a.tile_scheduler_metadata; k.num_sm_parts = a.num_sm_parts; k.num_splits = a.num_splits;
   k.out = a.out; k.o_stride_b = a.o_stride_b; k.o_stride_s = a.o_stride_s; k.o_stride_h = a.o_stride_h;
   k.softmax_lse = a.softmax_lse; k.lse_accum = a.lse_accum; k.o_accum = a.o_accum;
+  k.arrival_counters = (!push && !sparse) ? a.arrival_counters : nullptr;
   if (push) {
     k.force_partial = 1;
     k.push_slot = push->slot; k.push_num_dst = push->num_dst; k.push_epoch = push->epoch; k.push_counter = push->counter;
@@ -259,6 +260,8 @@ static int decode_impl(const fmla_decode_params* P, const fmla_peer_push* push, 
   }
   if (push) {
     e = fmla::launch_decode_combine_push(k, s);
+  } else if (!sparse && fmla::decode_dense_merges_in_kernel(k)) {
+    e = cudaSuccess;      // the last CTA to deliver a partial of a request has merged it
   } else {
     e = fmla::launch_decode_combine(k, s);
   }

@@ -38,6 +38,7 @@ struct DecodeKernelParams {
   int indices_logical;         // sparse decode: indices are token positions, mapped through block_table in the kernel
   int force_partial;
   int l2_prefetch_dist;        // pair kernel: cache pages this many blocks ahead are pulled into L2 (0 = off)
+  int* arrival_counters;       // pair kernel: per (request, query token, 64-head tile) arrivals of split partials; zero on entry and exit
   int push_slot, push_num_dst;
   float* push_o[8];            // [num_slots][b * h_k * rows][512]
   float* push_lse[8];          // [num_slots][b * h_k * rows], base 2
@@ -101,6 +102,8 @@ cudaError_t read_decode_tc_status(int* host_status, bool reset);
 // dense decode as a CTA pair (mla_pair.cu): 128 heads per pair, tcgen05 cta_group::2; used by
 // launch_decode_dense_tc whenever the heads per kv head are a multiple of 128
 bool decode_dense_pair_applies(const DecodeKernelParams& p);
+// true when launch_decode_dense_tc will merge the split partials inside the attention kernel (no merge launch needed)
+bool decode_dense_merges_in_kernel(const DecodeKernelParams& p);
 cudaError_t launch_decode_dense_pair(const DecodeKernelParams& p, cudaStream_t stream);
 cudaError_t read_decode_pair_status(int* host_status, bool reset);
 // Merge of split partials for a decode call (reads num_splits; skips unsplit requests).

@@ -611,6 +611,65 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
           p.lse_accum[part_row] = inv == 0.f ? neg_inf() : log2f(l) + m_used;
         }
       }
+      // ---- merge of a split request by whoever delivers its last partial ----------------
+      // Every CTA that has written a partial of (request, query token, this 64-head tile) counts itself in; the one
+      // that completes the count reads all partials back (they were written during this kernel: coherent loads)
+      // and writes the final rows, math of csrc/smxx/mla_combine.cu:71-107, 128-151.  The counter returns to zero.
+      if (!r.no_split && p.arrival_counters != nullptr) {
+        __threadfence();
+        bar_sync(1, 128);
+        int* sMerge = reinterpret_cast<int*>(smem + MISC_OFF + 16);
+        if (tid == 0) {
+          const int lo = __ldg(p.num_splits + r.batch), nsp = __ldg(p.num_splits + r.batch + 1) - lo;
+          const int n_hb = p.hq_per_hk >> 6;
+          int* ctr = p.arrival_counters + (((int64_t)r.batch * p.s_q + tile.sq) * p.h_k + tile.kh) * n_hb + tile.hb;
+          const bool last = atomicAdd(ctr, 1) == nsp - 1;
+          if (last) *ctr = 0;
+          sMerge[0] = last ? nsp : 0;
+          sMerge[1] = lo;
+        }
+        bar_sync(1, 128);
+        const int nsp = sMerge[0], lo = sMerge[1];
+        if (nsp > 0) {
+          __threadfence();
+          const int64_t rows_per_slot = (int64_t)p.h_k * q_seq_per_hk;
+          for (int rr = 0; rr < 16; ++rr) {
+            const int row = warp * 16 + rr;                              // one warp per row, 16 rows per warp
+            const int64_t prow = ((int64_t)lo * p.h_k + tile.kh) * q_seq_per_hk + tile.sq * p.hq_per_hk + tile.hb * 64 + row;
+            const float* lse_p = p.lse_accum + prow;
+            float mx = neg_inf();
+            for (int i = lane; i < nsp; i += 32) mx = fmaxf(mx, __ldcv(lse_p + i * rows_per_slot));
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+            if (mx == neg_inf()) mx = 0.f;
+            float sum = 0.f;
+            for (int i = lane; i < nsp; i += 32) sum += exp2f(__ldcv(lse_p + i * rows_per_slot) - mx);
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            const float glse = (sum == 0.f || sum != sum) ? pos_inf() : log2f(sum) + mx;
+            const int hd = tile.head0 + row;
+            if (lane == 0) p.softmax_lse[((int64_t)r.batch * p.h_q + hd) * p.s_q + tile.sq] = glse * kLn2;
+            float4 acc[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int i = 0; i < nsp; ++i) {
+              const float w = exp2f(__ldcv(lse_p + i * rows_per_slot) - glse);
+              if (w == 0.f) continue;
+              const float4* src = reinterpret_cast<const float4*>(p.o_accum + (prow + i * rows_per_slot) * 512);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float4 v = __ldcv(src + j * 32 + lane);
+                acc[j].x += w * v.x; acc[j].y += w * v.y; acc[j].z += w * v.z; acc[j].w += w * v.w;
+              }
+            }
+            __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + r.batch * p.o_stride_b + tile.sq * p.o_stride_s + hd * p.o_stride_h;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint2*>(orow + (j * 32 + lane) * 4) =
+                  make_uint2(pack_16x2<F16>(acc[j].x, acc[j].y), pack_16x2<F16>(acc[j].z, acc[j].w));
+          }
+        }
+      }
     }
   }
 

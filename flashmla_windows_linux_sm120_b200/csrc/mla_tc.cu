@@ -688,6 +688,10 @@ static bool pair_kernel_enabled() {
   return on;
 }
 
+bool decode_dense_merges_in_kernel(const DecodeKernelParams& p) {
+  return p.topk < 0 && decode_dense_pair_applies(p) && pair_kernel_enabled() && p.arrival_counters != nullptr && !p.force_partial;
+}
+
 cudaError_t launch_decode_dense_tc(const DecodeKernelParams& p, cudaStream_t stream) {
   if (decode_dense_pair_applies(p) && pair_kernel_enabled()) return launch_decode_dense_pair(p, stream);
   TcParams P = {};

@@ -22,6 +22,21 @@ def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+# Arrival counters of the in-kernel merge of split requests (fmla_decode_params.arrival_counters): zero on entry,
+# left zero by the kernel, so one array per (device, stream) is allocated once and reused -- calls on one stream
+# are ordered, calls on different streams get different arrays.
+_arrival_counters = {}
+
+
+def _counters_for(t: torch.Tensor, n: int) -> torch.Tensor:
+    key = (t.device.index, _stream(t))
+    buf = _arrival_counters.get(key)
+    if buf is None or buf.numel() < n:
+        buf = torch.zeros((max(n, 4096),), dtype=torch.int32, device=t.device)
+        _arrival_counters[key] = buf
+    return buf
+
+
 def _require(cond: bool, msg: str) -> None:
     if not cond:
         raise RuntimeError(msg)
@@ -132,6 +147,8 @@ def fwd_kvcache_mla(q: torch.Tensor, kcache: torch.Tensor, head_size_v: int, seq
         p.num_splits = num_splits.data_ptr()
         p.out, p.o_stride_b, p.o_stride_s, p.o_stride_h = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
         p.softmax_lse, p.lse_accum, p.o_accum = lse.data_ptr(), lse_accum.data_ptr(), o_accum.data_ptr()
+        if not sparse and (h_q // h_k) % 128 == 0:
+            p.arrival_counters = _counters_for(q, b * s_q * (h_q // 64)).data_ptr()
         if profile_events is not None:
             p.profile_event_begin = profile_events[0].cuda_event
             p.profile_event_end = profile_events[1].cuda_event

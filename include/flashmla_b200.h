@@ -126,6 +126,13 @@ typedef struct fmla_decode_params {
    * block_table[b][p / 64] * 64 + p % 64; p < 0 or p >= seqlens_k[b] = padding).  No counterpart in the
    * reference, whose callers remap to physical slots first (README.md:176). */
   int32_t indices_logical;
+
+  /* optional, dense decode: b * s_q * (h_q / 64) int32 counters, ZERO on entry and left zero on return.  When
+   * given (and the heads per kv head are a multiple of 128), the CTA that writes the last partial of a split
+   * request also merges that request's partials, so no separate merge kernel is launched: the whole step is
+   * one kernel.  Calls that may overlap on the GPU need separate counter arrays.  NULL = the merge runs as a
+   * second kernel (fmla's counterpart of csrc/smxx/mla_combine.cu).  No counterpart in the reference. */
+  int32_t* arrival_counters;
 } fmla_decode_params;
 
 /* Bytes of lse_accum and o_accum for a problem (host-side arithmetic only). */

@@ -1,8 +1,11 @@
-"""Integer oracle of the split-KV tile scheduler (test infrastructure only).
+"""Integer oracles of the split-KV tile scheduler (test infrastructure only).
 
-Follows csrc/smxx/get_mla_metadata.cu:25-88 (the single-warp kernel) and the
-partition sizing in csrc/pybind.cpp:288-380.  Pure Python integers: the outputs
-must match the CUDA scheduler bit for bit.
+`get_mla_metadata_ref` follows the reference, csrc/smxx/get_mla_metadata.cu:25-88 (the single-warp greedy walk)
+with the partition sizing of csrc/pybind.cpp:288-380; it documents the output contract and is the yardstick for
+the balance of any other schedule.  `schedule_cut_ref` is the integer statement of the schedule this library's
+kernel computes (proportional cuts of the cost line, snapped to request boundaries): the CUDA scheduler must
+match it bit for bit.  Both satisfy `check_schedule_invariants`, which is all a consumer relies on (the two
+tensors are opaque to callers, flash_mla_interface.py:116-163).
 """
 from __future__ import annotations
 
@@ -95,6 +98,100 @@ def get_mla_metadata_ref(seqlens_k: Sequence[int], num_sm_parts: int,
     assert now_idx == b and now_block == 0 and now_n_split_idx == 0, \
         "schedule did not cover the batch"              # :82
     return md, num_splits
+
+
+SNAP_BLOCKS = 0     # a cut this close to a request boundary moves onto it (0: only cuts inside an overhead stretch move)
+
+
+def schedule_cut_ref(seqlens_k: Sequence[int], num_sm_parts: int, topk: int = -1,
+                     block_size_n: int = BLOCK_SIZE_N,
+                     fixed_overhead_num_blocks: int = FIXED_OVERHEAD_NUM_BLOCKS,
+                     snap: int = SNAP_BLOCKS) -> Tuple[List[List[int]], List[int]]:
+    """The schedule of this library (same output contract as `get_mla_metadata_ref`).
+
+    Every request costs its block count (a zero-length request counts one block) plus a fixed overhead, laid out
+    on a line as [overhead | blocks] per request.  Cut k of num_sm_parts + 1 sits at k * pitch on that line.
+    With more requests than parts pitch = ceil(total / parts): every part then carries at most that many cost
+    units plus one overhead for starting in the middle of a request, the same bound as the reference's greedy
+    walk.  With at most one request per part pitch = ceil(total / parts) + overhead: the slack lets a batch of
+    similar requests fall one request per part instead of being cut everywhere (the last parts may then stay
+    empty).  A cut inside an overhead stretch (or within `snap` blocks of either end of a request's blocks)
+    moves to that request boundary.  Part k is everything between cuts k and k+1; equal cuts give an empty
+    part (begin_idx = batch).  Each cut depends only on the prefix sums, so the parts are computed
+    independently of each other, in parallel on the GPU.
+    """
+    b = len(seqlens_k)
+    lens = [int(s) if topk == -1 else int(topk) for s in seqlens_k]
+    real = [0 if l == 0 else cdiv(l, block_size_n) for l in lens]
+    nblk = [max(r, 1) for r in real]
+    pre = [0] * (b + 1)
+    for i in range(b):
+        pre[i + 1] = pre[i] + nblk[i] + fixed_overhead_num_blocks
+    total = pre[b]
+    pitch = cdiv(total, num_sm_parts) + (fixed_overhead_num_blocks if b <= num_sm_parts else 0)
+
+    def cut(k: int) -> Tuple[int, int]:
+        x = k * pitch
+        if k >= num_sm_parts or x >= total:
+            return (b, 0)
+        lo, hi = 0, b                     # last request r with pre[r] <= x
+        while hi - lo > 1:
+            mid = (lo + hi) // 2
+            if pre[mid] <= x:
+                lo = mid
+            else:
+                hi = mid
+        r = lo
+        off = x - pre[r] - fixed_overhead_num_blocks
+        if off <= snap:
+            return (r, 0)
+        if nblk[r] - off <= snap:
+            return (r + 1, 0)
+        return (r, off)
+
+    cuts = [cut(k) for k in range(num_sm_parts + 1)]
+    md = [[0] * TILE_SCHEDULER_METADATA_SIZE for _ in range(num_sm_parts)]
+    counts = [1] * b
+    for k in range(num_sm_parts):
+        (r0, o0), (r1, o1) = cuts[k], cuts[k + 1]
+        if (r0, o0) == (r1, o1):
+            md[k][0], md[k][2] = b, b - 1
+            continue
+        # distinct earlier cuts strictly inside request r0 = position of this part among the parts of r0
+        split = 0
+        if o0 > 0:
+            j = k
+            while j >= 1 and cuts[j][0] == r0 and cuts[j][1] > 0:
+                if cuts[j] != cuts[j - 1]:
+                    split += 1
+                j -= 1
+            counts[r0] = max(counts[r0], split + 1)
+        md[k][0], md[k][1], md[k][4] = r0, o0, split
+        if o1 > 0:
+            md[k][2], md[k][3] = r1, o1
+        else:
+            md[k][2], md[k][3] = r1 - 1, real[r1 - 1]
+    num_splits = [0] * (b + 1)
+    for i in range(b):
+        num_splits[i + 1] = num_splits[i] + counts[i]
+    return md, num_splits
+
+
+def max_part_cost(md, seqlens_k, topk: int = -1, block_size_n: int = BLOCK_SIZE_N,
+                  fixed_overhead_num_blocks: int = FIXED_OVERHEAD_NUM_BLOCKS) -> int:
+    """Largest cost of a part (blocks + overhead per visited request): what the slowest CTA has to do."""
+    b = len(seqlens_k)
+    lens = [int(s) if topk == -1 else int(topk) for s in seqlens_k]
+    nblk = [0 if l == 0 else cdiv(l, block_size_n) for l in lens]
+    worst = 0
+    for bi, bb, ei, eb in (row[:4] for row in md):
+        if bi >= b:
+            continue
+        c = 0
+        for r in range(bi, ei + 1):
+            c += (eb if r == ei else nblk[r]) - (bb if r == bi else 0) + fixed_overhead_num_blocks
+        worst = max(worst, c)
+    return worst
 
 
 def check_schedule_invariants(md, num_splits, seqlens_k, topk: int = -1,

@@ -32,13 +32,19 @@ def _gpu_metadata(seqlens, parts, topk):
     ([5] * 3, 37, 128),
     (list(range(3072, 5120, 16)), 74, -1),
     (list(range(1, 700)), 148, -1),
+    ([1 << 20], 74, -1),
+    ([4096] * 3000, 74, -1),                       # more requests than one pass of the block-wide scan
+    ([2048] * 64, 74, 2048),
 ])
 def test_scheduler_bit_exact(seqlens, parts, topk):
+    """The CUDA scheduler against the integer statement of its own algorithm (oracle.scheduler.schedule_cut_ref),
+    plus the invariants every consumer relies on; the balance is compared with the reference's greedy walk."""
     md, ns = _gpu_metadata(seqlens, parts, topk)
-    rmd, rns = scheduler.get_mla_metadata_ref(seqlens, parts, topk)
+    rmd, rns = scheduler.schedule_cut_ref(seqlens, parts, topk)
     assert md == rmd
     assert ns == rns
     scheduler.check_schedule_invariants(md, ns, seqlens, topk)
+    assert ns[-1] <= len(seqlens) + parts
 
 
 def test_num_sm_parts_formula():

@@ -35,6 +35,28 @@ def test_invariants_random():
         assert ns[-1] <= b + parts
 
 
+def test_cut_schedule_invariants_and_balance():
+    """The schedule this library computes: valid for any batch, never needs more partial slots than the caller
+    provides (batch + parts), and as balanced as the reference's greedy walk on the benchmark shapes."""
+    rng = random.Random(1)
+    for _ in range(300):
+        b = rng.choice([1, 2, 3, 5, 8, 64, 128, 200])
+        lens = [rng.choice([0, 1, 63, 64, 65, rng.randint(1, 9000), rng.randint(3072, 5120)]) for _ in range(b)]
+        parts = rng.choice([1, 2, 7, 37, 74, 148])
+        md, ns = scheduler.schedule_cut_ref(lens, parts)
+        scheduler.check_schedule_invariants(md, ns, lens)
+        assert ns[-1] <= b + parts
+    lens = [rng.randint(3072, 5120) for _ in range(128)]
+    for parts in (74, 37):
+        ours = scheduler.max_part_cost(scheduler.schedule_cut_ref(lens, parts)[0], lens)
+        theirs = scheduler.max_part_cost(scheduler.get_mla_metadata_ref(lens, parts)[0], lens)
+        assert ours <= theirs + 1
+    md, ns = scheduler.schedule_cut_ref([2048] * 64, 74, topk=2048)     # one request per part, nothing split
+    assert ns[-1] == 64 and scheduler.max_part_cost(md, [2048] * 64, 2048) == 37
+    md, ns = scheduler.schedule_cut_ref([1 << 20], 8)                    # one long context over 8 parts
+    assert ns == [0, 8] and [row[4] for row in md] == list(range(8))
+
+
 def test_num_sm_parts():
     assert scheduler.num_sm_parts_ref(148, 128, 1, 128, False) == 74
     assert scheduler.num_sm_parts_ref(148, 256, 1, 128, False) == 37
