@@ -66,6 +66,7 @@ __device__ __forceinline__ void combine_row(int nparts, LseAt lse_at, OAt o_at, 
 // in final form by the attention kernel and are skipped (mla_combine.cu:30-32).
 __global__ void __launch_bounds__(kCombineWarps * 32) decode_combine_kernel(const __grid_constant__ DecodeKernelParams p) {
   extern __shared__ float s_weights[];  // [8][num_sm_parts]
+  pdl_wait();                           // launched as a programmatic dependent of the attention kernel
   const int batch = blockIdx.x;
   const int lo = __ldg(p.num_splits + batch), hi = __ldg(p.num_splits + batch + 1);
   const int nparts = hi - lo;
@@ -255,8 +256,19 @@ cudaError_t launch_decode_combine(const DecodeKernelParams& p, cudaStream_t stre
   dim3 grid(p.b, (rows + kCombineWarps - 1) / kCombineWarps);
   const size_t smem = sizeof(float) * kCombineWarps * p.num_sm_parts;
   if (cudaError_t e = allow_dynamic_smem(decode_combine_kernel, smem); e != cudaSuccess) return e;
-  decode_combine_kernel<<<grid, kCombineWarps * 32, smem, stream>>>(p);
-  return cudaGetLastError();
+  // programmatic dependent launch: the blocks may become resident while the attention kernel drains and start
+  // the moment it has completed (they wait in pdl_wait()), instead of being launched after it
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kCombineWarps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, decode_combine_kernel, p);
 }
 
 cudaError_t launch_combine_partials(const float* lse_accum, const float* o_accum, int num_parts, int rows, void* out,

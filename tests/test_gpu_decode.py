@@ -208,3 +208,24 @@ def test_argument_errors():
         fm.flash_mla_with_kvcache(d.q.cuda(), d.blocked_k.cuda(), d.block_table.cuda().long(), lens, 512, md, ns)
     with pytest.raises(RuntimeError):   # query and cache must have one dtype
         fm.flash_mla_with_kvcache(d.q.cuda().half(), d.blocked_k.cuda(), d.block_table.cuda(), lens, 512, md, ns)
+
+
+@pytest.mark.parametrize("s_q", [1, 2])
+def test_dense_decode_merge_in_kernel_is_bit_equal_to_the_merge_kernel(s_q):
+    """128 heads: the CTA pair kernel can merge split requests itself (arrival counters) instead of leaving it to
+    the dependent-launched merge kernel.  Same partials, same order of summation: identical bits, twice in a row
+    (the counters must have returned to zero)."""
+    from flashmla_windows_linux_sm120_b200 import cuda_sm100
+    fm = _api()
+    t = gen.DecodeCase(b=6, s_q=s_q, s_k=2500, is_varlen=True, is_causal=True, h_q=128, seed=5)
+    d = gen.make_decode_case(t)
+    lens, bt, cache, q = d.cache_seqlens.cuda(), d.block_table.cuda(), d.blocked_k.cuda(), d.q.cuda()
+    md, ns = fm.get_mla_metadata(lens, t.s_q * t.h_q, 1)
+    assert int(ns[-1]) > t.b
+    ref = cuda_sm100.fwd_kvcache_mla(q, cache, 512, lens, bt, 576 ** -0.5, True, md, ns, merge_in_kernel=False)
+    for _ in range(2):
+        got = cuda_sm100.fwd_kvcache_mla(q, cache, 512, lens, bt, 576 ** -0.5, True, md, ns, merge_in_kernel=True)
+        torch.cuda.synchronize()
+        assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1])
+    r_out, r_lse = decode.decode_ref(d.cache_seqlens, d.block_table, d.q, d.blocked_k, 512, True)
+    U.assert_out_lse(got[0].cpu(), got[1].cpu(), r_out, r_lse, what=f"merge in kernel s_q={s_q}")
