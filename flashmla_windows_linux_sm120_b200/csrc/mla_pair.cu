@@ -62,8 +62,9 @@ constexpr int P_OFF = V_OFF + 2 * kVStageBytes;   // 2 x [64 x 64]
 constexpr int BAR_OFF = P_OFF + 2 * kChunkBytes;
 constexpr int MX_OFF = BAR_OFF + 256;             // float [3][128] exchange
 constexpr int MISC_OFF = MX_OFF + 1536;
-constexpr int SMEM_BYTES = MISC_OFF + 64;
+constexpr int SMEM_BYTES = MISC_OFF + 128;
 static_assert(kQTmemChunks * kChunkBytes <= kKStages * kKStageBytes, "Q staging must fit into the K ring");
+static_assert(kQTmemChunks * kChunkBytes <= 2 * kVStageBytes, "Q staging must fit into the V ring (sparse prefill)");
 // leader-side barriers (waited on by the MMA warp of rank 0; arrivals come from both CTAs)
 // and per-CTA barriers (each CTA waits on its own copy; the leader's commits arrive on both copies)
 enum Bar { Q_FULL = 0, K_FULL0, K_FULL1, K_FULL2, V_FULL0, V_FULL1, S_EMPTY0, S_EMPTY1, P_FULL0, P_FULL1, O_EMPTY,
@@ -74,6 +75,8 @@ static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory limit per 
 static_assert(NUM_BARS * 8 <= 256, "barrier area too small");
 constexpr float kRescaleThreshold = 8.0f;
 constexpr int kThreads = 256;
+constexpr int kPrefillThreads = 320;       // two more gather warps (8, 9) in the sparse prefill mode
+constexpr int kGatherWarps = 3;
 }  // namespace ptc
 
 __device__ int g_decode_pair_status = 0;
@@ -142,12 +145,25 @@ __device__ __forceinline__ void pv_block_pair(uint32_t tmem_o, uint64_t desc_p_s
                       tc::desc_advance(desc_v_stage, h * 2 * kChunkBytes + s * 2048), idesc, (first && s == 0) ? 0u : 1u);
 }
 
-// grid (s_q * hq_per_hk / 64, h_k, parts), clusters of two CTAs along x; 256 threads
-template <bool F16>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(ptc::kThreads, 1)
+// 4 rows x 64 columns of a row-major [rows, 576] tensor, the rows given one by one (TMA gather); a row index
+// outside the tensor reads as zeros
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const void* tmap, int col, int r0, int r1, int r2, int r3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];\n" ::"r"(dst),
+      "l"(tmap), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar)
+      : "memory");
+}
+
+// Decode: grid (s_q * hq_per_hk / 64, h_k, parts), clusters of two CTAs along x; 256 threads.
+// PREFILL (sparse prefill forward, 128 heads): grid (2, lanes), every pair walks the query tokens lane, lane + lanes, ..;
+// the K / V parts of a 64-index block are gathered row by row with TMA (tile::gather4) from kv[s_kv, 576]
+// (tmap_k32 = tmap_v64 = the gather map), invalid indices read as zero rows and are masked through validity bits.
+template <bool F16, bool PREFILL>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PREFILL ? ptc::kPrefillThreads : ptc::kThreads, 1)
 mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_k32, const __grid_constant__ CUtensorMap tmap_v64) {
   using namespace ptc;
+  constexpr int WM = PREFILL ? kSparsePrefill : kDense;
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t sbase = smem_u32(smem);
   const uint32_t sQ = sbase + Q_OFF, sK = sbase + K_OFF, sV = sbase + V_OFF, sP = sbase + P_OFF;
@@ -167,11 +183,14 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     g_pair_span[(blockIdx.z * gridDim.x + blockIdx.x) * 2] = (long long)t;
   }
 #endif
-  const Tile tile = make_tile<kDense>(P);
+  const Tile tile = make_tile<WM>(P);
   if (tile.n_work == 0) return;                 // both CTAs of a pair see the same schedule row
   const bool misaligned = (sbase & 1023u) != 0;  // the swizzled tiles need a 1024-byte aligned base
   auto lbar = [&](int i) { return tc::mapa(bar(i), 0); };    // the leader's copy of barrier i
-  const float scale_log2 = p.scale_log2;
+  const float scale_log2 = PREFILL ? P.sp.scale_log2 : p.scale_log2;
+  // prefill: validity bits of the 64 tokens of a block, ring of 6 blocks x 2 words (the K loader runs at most three
+  // blocks ahead of S, and S of block g+3 is only issued after the softmax has read block g+1)
+  volatile uint32_t* sValid = reinterpret_cast<volatile uint32_t*>(smem + MISC_OFF + 32);
 
   if (tid == 0) {
     tc::mbar_init(bar(Q_FULL), 2);
@@ -185,7 +204,12 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     tc::mbar_init(bar(P_FULL0), 256);
     tc::mbar_init(bar(P_FULL1), 256);
     tc::mbar_init(bar(O_EMPTY), 256);
-    for (int i = Q_EMPTY; i < NUM_BARS; ++i) tc::mbar_init(bar(i), 1);
+    // prefill: a K stage is free again once its S has completed (one commit) and the value columns forwarded out of
+    // it have landed in both CTAs (one arrival from the V relay of each CTA)
+    // and a K stage has landed when every lane of the gather warps has arrived by hardware, plus the thread that
+    // published the validity bits
+    for (int i = Q_EMPTY; i < NUM_BARS; ++i)
+      tc::mbar_init(bar(i), !PREFILL ? 1 : (i >= K_EMPTY0 && i <= K_EMPTY2) ? 3 : (i >= K_LAND0 && i <= K_LAND2) ? kGatherWarps * 32 + 1 : 1);
     tc::fence_mbar_init();
     *sAbort = 0;
     if (misaligned) tc::report_status(status, 30);
@@ -200,6 +224,73 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
 
   if (misaligned) {
     // nothing was issued; fall through to the common exit
+  } else if ((warp == 4 || warp >= 8) && PREFILL) {
+    // ================================ Q and K loader, sparse prefill ===================
+    // The CTA's 32 token rows of a block (32 x 1152 bytes) are gathered with 16-byte cp.async copies by three warps
+    // (4, 8, 9): 72 warp instructions per block, 24 per warp, consecutive lanes on consecutive pieces of a row.
+    // A warp keeps only a bounded number of such copies in flight (about 8 bytes per clock at L2 latency), and the
+    // TMA engine gathers rows no faster than ~11 bytes per clock (tile::gather4, one 4-row copy per ~46 clocks),
+    // hence several warps.  Each lane's copies arrive on the landing barrier by hardware (arrive.noinc).
+    // Nothing else of the block is read from global memory: the value operand of both CTAs is put together from
+    // these rows by shared-memory copies (warp 6), which also loads Q: the gather runs ahead into the next query
+    // token while the current one drains.  Warp 4 publishes the validity bits of the 64 indices.  An index outside
+    // the tensor (negative or >= s_kv) leaves a zero row.
+    int g = 0;
+    bool alive = true;
+    const int s_kv = P.sp.s_kv;
+    const int gw = warp == 4 ? 0 : warp - 7;                 // 0, 1, 2
+    const char* kvb = reinterpret_cast<const char*>(P.sp.kv);
+    const int64_t row_bytes = P.sp.kv_stride_s * 2;
+    for (int wi = 0; wi < tile.n_work && alive; ++wi) {
+      const Work r = get_work<WM>(P, tile, wi);
+      // the indices of a block are read one block ahead of their use: their latency would otherwise be paid in
+      // every turn of this loop
+      const int* my_idx = r.idx + 32 * static_cast<int>(rank) + lane;
+      int mine_next = r.blk_lo < r.blk_hi ? __ldg(my_idx + r.blk_lo * 64) : -1, i0_next = -1, i1_next = -1;
+      if (warp == 4 && r.blk_lo < r.blk_hi) {
+        i0_next = __ldg(r.idx + r.blk_lo * 64 + lane);
+        i1_next = __ldg(r.idx + r.blk_lo * 64 + 32 + lane);
+      }
+      for (int blk = r.blk_lo; blk < r.blk_hi && alive; ++blk, ++g) {
+        const int st = g % kKStages;
+        int mine = mine_next;                                                          // row `lane` of this CTA's part
+        const int i0 = i0_next, i1 = i1_next;
+        if (blk + 1 < r.blk_hi) {
+          mine_next = __ldg(my_idx + (blk + 1) * 64);
+          if (warp == 4) {
+            i0_next = __ldg(r.idx + (blk + 1) * 64 + lane);
+            i1_next = __ldg(r.idx + (blk + 1) * 64 + 32 + lane);
+          }
+        }
+        if (mine < 0 || mine >= s_kv) mine = -1;
+        uint32_t b0 = 0, b1 = 0;
+        if (warp == 4) {
+          b0 = __ballot_sync(0xffffffffu, i0 >= 0 && i0 < s_kv);
+          b1 = __ballot_sync(0xffffffffu, i1 >= 0 && i1 < s_kv);
+        }
+        alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(K_EMPTY0 + st), ((g / kKStages) & 1) ^ 1, status, 102));
+        if (!alive) break;
+        if (warp == 4 && lane == 0) FMLA_PTRACE_AT(g, 0);
+        const uint32_t dst = sK + st * kKStageBytes;
+#ifndef FMLA_EXP_NO_GATHER     // timing experiment only: results are wrong
+#pragma unroll 8
+        for (int it = 0; it < 24; ++it) {
+          const int e = (gw * 24 + it) * 32 + lane;              // piece e of 32 rows x 72 pieces of 16 bytes
+          const int row = e / 72, piece = e - row * 72;
+          const int idx = __shfl_sync(0xffffffffu, mine, row);
+          const bool ok = idx >= 0;
+          const char* src = kvb + (ok ? (int64_t)idx * row_bytes + piece * 16 : 0);
+          cp_async16(dst + (piece >> 3) * kKChunkBytes + row * 128 + (((piece & 7) ^ (row & 7)) << 4), src, ok);
+        }
+#endif
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar(K_LAND0 + st)) : "memory");
+        if (warp == 4 && lane == 0) {
+          sValid[(g % 6) * 2] = b0;
+          sValid[(g % 6) * 2 + 1] = b1;
+          tc::mbar_arrive(bar(K_LAND0 + st));
+        }
+      }
+    }
   } else if (warp == 4) {
     // ================================ Q and K loader ===================================
     if (tc::elect_one()) {
@@ -208,7 +299,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
       int g = 0, req = 0;
       bool alive = true;
       for (int wi = 0; wi < tile.n_work && alive; ++wi) {
-        const Work r = get_work<kDense>(P, tile, wi);
+        const Work r = get_work<WM>(P, tile, wi);
         if (r.blk_hi == r.blk_lo) continue;
         alive = tc::mbar_wait(bar(Q_EMPTY), (req & 1) ^ 1, status, 101);
         if (!alive) break;
@@ -219,7 +310,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
 #pragma unroll
         for (int c = 0; c < 9; ++c)
           tc::tma_load_4d(c < kQTmemChunks ? sK + c * kChunkBytes : sQ + (c - kQTmemChunks) * kChunkBytes, &tmap_q, c * 64, tile.head0,
-                          tile.sq, r.batch, q_bar);
+                          PREFILL ? r.batch : tile.sq, PREFILL ? 0 : r.batch, q_bar);
         // the K ring may be refilled once the leader has copied the staged chunks into tensor memory
         alive = tc::mbar_wait(bar(QT_DONE), req & 1, status, 107);
         if (!alive) break;
@@ -257,6 +348,68 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         ++req;
       }
     }
+  } else if (warp == 6 && PREFILL) {
+    // ================================ K relay and V forwarder, sparse prefill ==========
+    // The gathered rows of this CTA (32 tokens x 576 columns) hold the value columns of those tokens for both CTAs.
+    // Once they have landed, each 64-column chunk of the value part goes, as one 4 KB shared-memory copy, to the
+    // V stage of the CTA whose output columns it belongs to (its own or, over the cluster's shared-memory network,
+    // the peer's): rows [32 * rank, 32 * rank + 32) of that stage's chunk.  The 128-byte swizzle pattern repeats every
+    // 1024 bytes, so a chunk moves as it is.  Global memory and L2 are read once per pair and block.
+    // Q of a query token: chunks 6..8 go to their place, chunks 0..5 are staged in the V ring (48 of its 64 KB) until
+    // the leader has copied them into tensor memory.  Loaded once every S of the previous token has completed (Q in
+    // shared and tensor memory free) and its last two P V have released the V stages.
+    if (tc::elect_one()) {
+      tc::prefetch_tensormap(&tmap_q);
+      int g = 0, req = 0;
+      bool alive = true;
+      for (int wi = 0; wi < tile.n_work && alive; ++wi) {
+        const Work r = get_work<WM>(P, tile, wi);
+        if (r.blk_hi == r.blk_lo) continue;
+        alive = tc::mbar_wait(bar(Q_EMPTY), (req & 1) ^ 1, status, 101);
+        for (int gg = max(0, g - 2); gg < g && alive; ++gg) alive = tc::mbar_wait(bar(V_EMPTY0 + (gg & 1)), (gg >> 1) & 1, status, 103);
+        if (!alive) break;
+        {
+          const uint32_t q_bar = rank == 0 ? bar(Q_FULL) : bar(Q_LAND);
+          tc::mbar_arrive_expect_tx(q_bar, kQBytes);
+#pragma unroll
+          for (int c = 0; c < 9; ++c)
+            tc::tma_load_4d(c < kQTmemChunks ? sV + c * kChunkBytes : sQ + (c - kQTmemChunks) * kChunkBytes, &tmap_q, c * 64, tile.head0,
+                            r.batch, 0, q_bar);
+        }
+        alive = tc::mbar_wait(bar(QT_DONE), req & 1, status, 107);       // in both CTAs: the commit goes to both
+        ++req;
+        for (int blk = r.blk_lo; blk < r.blk_hi && alive; ++blk, ++g) {
+          const int kst = g % kKStages, vst = g & 1;
+          alive = tc::mbar_wait(bar(K_LAND0 + kst), (g / kKStages) & 1, status, 112);
+          if (!alive) break;
+          tc::fence_proxy_async_smem();        // rows written by cp.async -> bulk copies and the tensor pipe
+          tc::mbar_arrive_cluster(lbar(K_FULL0 + kst));
+          // P V of block g-2 has completed in both CTAs (its commit goes to both): both V stages are free
+          alive = tc::mbar_wait(bar(V_EMPTY0 + vst), ((g >> 1) & 1) ^ 1, status, 103);
+          if (!alive) break;
+          FMLA_PTRACE_AT(g, 12);
+#ifdef FMLA_EXP_NO_FWD          // timing experiment only: results are wrong
+          tc::mbar_arrive(bar(V_LAND0 + vst));
+          continue;
+#endif
+          tc::mbar_arrive_expect_tx(bar(V_LAND0 + vst), kVStageBytes);      // 16 KB from this CTA, 16 KB from the peer
+#pragma unroll
+          for (int d = 0; d < 2; ++d) {
+            const uint32_t dest = rank ^ static_cast<uint32_t>(d);
+            const uint32_t dst_bar = tc::mapa(bar(V_LAND0 + vst), dest);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int chunk = (i >> 1) * 4 + 2 * static_cast<int>(dest) + (i & 1);     // value columns 64*chunk ..
+              const uint32_t src = sK + kst * kKStageBytes + chunk * kKChunkBytes;
+              const uint32_t dst = tc::mapa(sV + vst * kVStageBytes + i * kChunkBytes + rank * kKChunkBytes, dest);
+              asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+                           "r"(src), "r"(kKChunkBytes), "r"(dst_bar)
+                           : "memory");
+            }
+          }
+        }
+      }
+    }
   } else if (warp == 6) {
     // ================================ V loader =========================================
     if (tc::elect_one()) {
@@ -264,7 +417,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
       int g = 0;
       bool alive = true;
       for (int wi = 0; wi < tile.n_work && alive; ++wi) {
-        const Work r = get_work<kDense>(P, tile, wi);
+        const Work r = get_work<WM>(P, tile, wi);
         const int* bt = p.block_table + r.batch * p.block_table_stride_b;
         for (int blk = r.blk_lo; blk < r.blk_hi; ++blk, ++g) {
           const int st = g & 1;
@@ -291,12 +444,12 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     int g = 0;
     bool alive = true;
     for (int wi = 0; wi < tile.n_work && alive; ++wi) {
-      const Work r = get_work<kDense>(P, tile, wi);
+      const Work r = get_work<WM>(P, tile, wi);
       for (int blk = r.blk_lo; blk < r.blk_hi && alive; ++blk, ++g) {
         const int st = g & 1;
         alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(V_LAND0 + st), (g >> 1) & 1, status, 104));
         if (!alive) break;
-        const int rows_valid = r.seqlen - blk * 64;
+        const int rows_valid = PREFILL ? 64 : r.seqlen - blk * 64;
         if (rows_valid < 64) {
           unsigned char* stage = smem + V_OFF + st * kVStageBytes;
           const int nrows = 64 - rows_valid;
@@ -307,7 +460,14 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
           tc::fence_proxy_async_smem();
           __syncwarp();
         }
-        if (lane == 0) { FMLA_PTRACE_AT(g, 13); tc::mbar_arrive_cluster(lbar(V_FULL0 + st)); }
+        if (lane == 0) {
+          FMLA_PTRACE_AT(g, 13);
+          tc::mbar_arrive_cluster(lbar(V_FULL0 + st));
+          if constexpr (PREFILL) {      // every copy out of K stage g % 3 of either CTA into this V stage has completed
+            tc::mbar_arrive_cluster(tc::mapa(bar(K_EMPTY0 + g % kKStages), 0));
+            tc::mbar_arrive_cluster(tc::mapa(bar(K_EMPTY0 + g % kKStages), 1));
+          }
+        }
       }
     }
   } else if (warp == 5 && rank != 0) {
@@ -315,12 +475,12 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     int g = 0, req = 0;
     bool alive = true;
     for (int wi = 0; wi < tile.n_work && alive; ++wi) {
-      const Work r = get_work<kDense>(P, tile, wi);
+      const Work r = get_work<WM>(P, tile, wi);
       if (r.blk_hi == r.blk_lo) continue;
       alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_LAND), req & 1, status, 111));
       if (!alive) break;
       if (lane == 0) tc::mbar_arrive_cluster(lbar(Q_FULL));
-      for (int blk = r.blk_lo; blk < r.blk_hi && alive; ++blk, ++g) {
+      for (int blk = r.blk_lo; blk < r.blk_hi && alive && !PREFILL; ++blk, ++g) {     // prefill: warp 6 relays K
         const int st = g % kKStages;
         alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(K_LAND0 + st), (g / kKStages) & 1, status, 112));
         if (alive && lane == 0) tc::mbar_arrive_cluster(lbar(K_FULL0 + st));
@@ -333,7 +493,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
       constexpr uint32_t idesc_s = tc::idesc_bf16_f32(128, 64, 0, 0, F16);
       constexpr uint32_t idesc_o = tc::idesc_bf16_f32(128, 256, 0, 1, F16);
       const uint64_t desc_q = tc::smem_desc_sw128(sQ, 16, 1024);             // A of S, chunks 6..8: K-major
-      const uint64_t desc_qstage = tc::smem_desc_sw128(sK, 16, 1024);        // chunks 0..5 of Q where the loader stages them
+      const uint64_t desc_qstage = tc::smem_desc_sw128(PREFILL ? sV : sK, 16, 1024);   // chunks 0..5 of Q where the loader stages them
       const uint64_t desc_k = tc::smem_desc_sw128(sK, 16, 1024);             // B of S: K-major, 32 rows per CTA (stage 0)
       const uint64_t desc_p = tc::smem_desc_sw128(sP, 16, 1024);             // A of PV: K-major
       const uint64_t desc_v = tc::smem_desc_sw128(sV, kChunkBytes, 1024);    // B of PV: MN-major, 64-wide column groups 8 KB apart
@@ -348,7 +508,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
       int seen_k = -1, seen_s = -1, seen_p = -1, seen_v = -1, after_issue = 0;
 #endif
       for (int wi = 0; wi < tile.n_work && alive; ++wi) {
-        const Work r = get_work<kDense>(P, tile, wi);
+        const Work r = get_work<WM>(P, tile, wi);
         const int nblk = r.blk_hi - r.blk_lo;
         if (nblk == 0) continue;
         alive = __all_sync(0xffffffffu, tc::mbar_wait_cluster(bar(Q_FULL), req & 1, status, 105));
@@ -414,6 +574,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
             after_issue = 2;
 #endif
           } else if (js < nblk && (m & 0x18u) == 0x18u) {
+            if constexpr (PREFILL) tc::fence_proxy_async_smem();   // K rows came through cp.async
             tc::tc_fence_after();
             if (lane == 0) { FMLA_PTRACE_AT(gs, 2); FMLA_GTRACE_AT(gs, 0, 3); }
             if (tc::elect_one()) {
@@ -455,7 +616,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     int g = 0, req = 0;
     bool aborted = false;        // uniform over the 128 softmax threads: only read right after a bar_sync
     for (int wi = 0; wi < tile.n_work; ++wi) {
-      const Work r = get_work<kDense>(P, tile, wi);
+      const Work r = get_work<WM>(P, tile, wi);
       const int nblk = r.blk_hi - r.blk_lo;
       float m_run = neg_inf();     // running maximum (base-2 scaled logits)
       float m_used = 0.f;          // the maximum O and l are currently scaled with
@@ -478,8 +639,12 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         tc::mbar_arrive_cluster(l_s_empty0 + st * 8);
         if (tid == 0) { FMLA_PTRACE_AT(g, 7); FMLA_GTRACE_AT(g, rank, 1); }
 
-        const int tok0 = (r.blk_lo + j) * 64 + th * 32;
-        if (tok0 + 32 > r.border) vbits = tok0 >= r.border ? 0u : (0xffffffffu >> (32 - (r.border - tok0)));
+        if constexpr (PREFILL) {
+          vbits = sValid[(g % 6) * 2 + th];
+        } else {
+          const int tok0 = (r.blk_lo + j) * 64 + th * 32;
+          if (tok0 + 32 > r.border) vbits = tok0 >= r.border ? 0u : (0xffffffffu >> (32 - (r.border - tok0)));
+        }
         if (vbits != 0xffffffffu) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
@@ -564,11 +729,13 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         if (!tc::mbar_wait(bar(O_FULL), req & 1, status, 110)) { *sAbort = 1; have_o = false; }
         tc::tc_fence_after();
       }
-      const int q_seq_per_hk = p.s_q * p.hq_per_hk;
-      const int row_in_group = tile.sq * p.hq_per_hk + tile.hb * 64 + r_row;   // regrouped row index within the kv head
-      __nv_bfloat16* o_final = reinterpret_cast<__nv_bfloat16*>(p.out) + r.batch * p.o_stride_b + tile.sq * p.o_stride_s + head * p.o_stride_h;
-      const int64_t part_row = ((int64_t)r.split_slot * p.h_k + tile.kh) * q_seq_per_hk + row_in_group;
-      float* o_part = p.o_accum + part_row * 512;
+      const int q_seq_per_hk = PREFILL ? 0 : p.s_q * p.hq_per_hk;
+      const int row_in_group = PREFILL ? 0 : tile.sq * p.hq_per_hk + tile.hb * 64 + r_row;   // regrouped row index within the kv head
+      __nv_bfloat16* o_final = PREFILL
+          ? reinterpret_cast<__nv_bfloat16*>(P.sp.out) + ((int64_t)r.batch * P.sp.h_q + head) * 512
+          : reinterpret_cast<__nv_bfloat16*>(p.out) + r.batch * p.o_stride_b + tile.sq * p.o_stride_s + head * p.o_stride_h;
+      const int64_t part_row = PREFILL ? 0 : ((int64_t)r.split_slot * p.h_k + tile.kh) * q_seq_per_hk + row_in_group;
+      float* o_part = PREFILL ? nullptr : p.o_accum + part_row * 512;
 #pragma unroll 1
       for (int c = 0; c < 8; ++c) {
         uint32_t ov[32];
@@ -605,7 +772,13 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         ++req;
       }
       if (tid == 0) FMLA_PTRACE_AT(g - 1, 15);
-      if (th == 0) {
+      if constexpr (PREFILL) {
+        if (th == 0) {      // base-2 quantities; a row without any valid index gives out 0, max_logits -inf, lse -inf
+          const int64_t o = (int64_t)r.batch * P.sp.h_q + head;
+          P.sp.max_logits[o] = inv == 0.f ? neg_inf() : m_run;
+          P.sp.lse[o] = inv == 0.f ? neg_inf() : log2f(l) + m_used;
+        }
+      } else if (th == 0) {
         if (r.no_split) {
           p.softmax_lse[((int64_t)r.batch * p.h_q + head) * p.s_q + tile.sq] = inv == 0.f ? pos_inf() : (log2f(l) + m_used) * kLn2;
         } else {
@@ -616,7 +789,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
       // Every CTA that has written a partial of (request, query token, this 64-head tile) counts itself in; the one
       // that completes the count reads all partials back (they were written during this kernel: coherent loads)
       // and writes the final rows, math of csrc/smxx/mla_combine.cu:71-107, 128-151.  The counter returns to zero.
-      if (!r.no_split && p.arrival_counters != nullptr) {
+      if (!PREFILL && !r.no_split && p.arrival_counters != nullptr) {
         __threadfence();
         bar_sync(1, 128);
         int* sMerge = reinterpret_cast<int*>(smem + MISC_OFF + 16);
@@ -716,6 +889,41 @@ static bool pair_map_4d(CUtensorMap* m, const void* base, uint64_t d1, uint64_t 
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// kv [s_kv][576] (row stride in elements) as a 2-D map for row gathers: box = 64 columns x 1 row
+static bool pair_gather_map(CUtensorMap* m, const void* base, uint64_t rows, int64_t row_stride) {
+  EncodeTiledFn enc = pair_encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {576, rows};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride) * 2};
+  cuuint32_t box[2] = {64, 1};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool sparse_prefill_pair_applies(const SparsePrefillKernelParams& sp) { return sp.h_q == 128; }
+
+cudaError_t launch_sparse_prefill_pair(const SparsePrefillKernelParams& sp, cudaStream_t stream) {
+  TcParams P = {};
+  P.sp = sp;
+  CUtensorMap tq, tg;
+  // q [s_q][h_q][576] as (col, head, token, 1)
+  if (!pair_map_4d(&tq, sp.q, sp.h_q, sp.s_q, 1, sp.q_stride_h, sp.q_stride_s, sp.q_stride_s * sp.s_q, 64, 1)) return cudaErrorInvalidValue;
+  if (!pair_gather_map(&tg, sp.kv, sp.s_kv, sp.kv_stride_s)) return cudaErrorInvalidValue;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
+  const int lanes = max(1, min(sp.s_q, sms / 2));
+  auto kern = mla_pair_kernel<false, true>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ptc::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  kern<<<dim3(2, lanes, 1), ptc::kPrefillThreads, ptc::SMEM_BYTES, stream>>>(P, tq, tg, tg);
+  return cudaGetLastError();
+}
+
 bool decode_dense_pair_applies(const DecodeKernelParams& p) { return p.hq_per_hk % 128 == 0; }
 
 cudaError_t launch_decode_dense_pair(const DecodeKernelParams& p, cudaStream_t stream) {
@@ -736,7 +944,7 @@ cudaError_t launch_decode_dense_pair(const DecodeKernelParams& p, cudaStream_t s
   const dim3 grid(p.s_q * n_hb, p.h_k, p.num_sm_parts);
   static bool attr_set[2] = {false, false};      // idempotent, so a race between threads is harmless
   if (p.is_f16) {
-    auto kern = mla_pair_kernel<true>;
+    auto kern = mla_pair_kernel<true, false>;
     if (!attr_set[1]) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ptc::SMEM_BYTES);
       if (e != cudaSuccess) return e;
@@ -744,7 +952,7 @@ cudaError_t launch_decode_dense_pair(const DecodeKernelParams& p, cudaStream_t s
     }
     kern<<<grid, ptc::kThreads, ptc::SMEM_BYTES, stream>>>(P, tq, tk, tv);
   } else {
-    auto kern = mla_pair_kernel<false>;
+    auto kern = mla_pair_kernel<false, false>;
     if (!attr_set[0]) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ptc::SMEM_BYTES);
       if (e != cudaSuccess) return e;

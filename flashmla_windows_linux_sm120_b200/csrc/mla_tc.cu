@@ -730,6 +730,7 @@ cudaError_t launch_decode_sparse_tc(const DecodeKernelParams& p, cudaStream_t st
 }
 
 cudaError_t launch_sparse_prefill_tc(const SparsePrefillKernelParams& sp, cudaStream_t stream) {
+  if (sparse_prefill_pair_applies(sp) && pair_kernel_enabled()) return launch_sparse_prefill_pair(sp, stream);
   TcParams P = {};
   P.sp = sp;
   CUtensorMap tq;
