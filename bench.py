@@ -220,7 +220,7 @@ class DenseDecode(Workload):
     """Dense BF16 MLA decode at the DeepSeek-V3 shape."""
     metric, unit, dtype = "dense_bf16_mla_decode_bandwidth", "GB/s", "bf16"
     bound = "hbm"
-    kernel_name = "mla_tc_kernel<kDense>"
+    kernel_name = "mla_pair_kernel<decode> (+ decode_combine_kernel)"
     launches_per_step = 2          # split-KV attention + combine
     e2e_buffers = 2
     e2e_max_steps = 10 ** 9
@@ -423,7 +423,7 @@ class SparsePrefill(Workload):
     metric, unit, dtype = "sparse_mla_prefill_fwd_tflops", "TFLOP/s", "bf16"
     bound = "tensor"
     key = "sparse_prefill"
-    kernel_name = "mla_tc_kernel<kSparsePrefill>"
+    kernel_name = "mla_pair_kernel<prefill>"
     launches_per_step = 1
     scaling = "strong"
     sharding = "query tokens sharded (kv replicated), no collective"
@@ -647,7 +647,7 @@ class KVShardedDecode(Workload):
     metric, unit, dtype = "kv_sharded_decode_bandwidth", "GB/s", "bf16"
     bound = "hbm"
     key = "kv_sharded_decode"
-    kernel_name = "mla_tc_kernel<kDense> + push/merge"
+    kernel_name = "mla_pair_kernel<decode> + push/merge"
     launches_per_step = 3
     scaling = "strong"
     sharding = "KV pages of one context sharded along the sequence; peer-memory merge of O / LSE"

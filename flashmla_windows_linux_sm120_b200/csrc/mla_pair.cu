@@ -75,8 +75,11 @@ static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory limit per 
 static_assert(NUM_BARS * 8 <= 256, "barrier area too small");
 constexpr float kRescaleThreshold = 8.0f;
 constexpr int kThreads = 256;
-constexpr int kPrefillThreads = 320;       // two more gather warps (8, 9) in the sparse prefill mode
-constexpr int kGatherWarps = 3;
+#ifndef FMLA_GATHER_WARPS
+#define FMLA_GATHER_WARPS 4
+#endif
+constexpr int kGatherWarps = FMLA_GATHER_WARPS;                 // sparse prefill: warp 4 and warps 8 .. 6 + kGatherWarps
+constexpr int kPrefillThreads = (7 + kGatherWarps) * 32;
 }  // namespace ptc
 
 __device__ int g_decode_pair_status = 0;
@@ -145,19 +148,11 @@ __device__ __forceinline__ void pv_block_pair(uint32_t tmem_o, uint64_t desc_p_s
                       tc::desc_advance(desc_v_stage, h * 2 * kChunkBytes + s * 2048), idesc, (first && s == 0) ? 0u : 1u);
 }
 
-// 4 rows x 64 columns of a row-major [rows, 576] tensor, the rows given one by one (TMA gather); a row index
-// outside the tensor reads as zeros
-__device__ __forceinline__ void tma_gather4(uint32_t dst, const void* tmap, int col, int r0, int r1, int r2, int r3, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];\n" ::"r"(dst),
-      "l"(tmap), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar)
-      : "memory");
-}
-
 // Decode: grid (s_q * hq_per_hk / 64, h_k, parts), clusters of two CTAs along x; 256 threads.
 // PREFILL (sparse prefill forward, 128 heads): grid (2, lanes), every pair walks the query tokens lane, lane + lanes, ..;
-// the K / V parts of a 64-index block are gathered row by row with TMA (tile::gather4) from kv[s_kv, 576]
-// (tmap_k32 = tmap_v64 = the gather map), invalid indices read as zero rows and are masked through validity bits.
+// each CTA gathers its 32 token rows of a 64-index block from kv[s_kv, 576] with cp.async and the value operand is
+// forwarded from those rows (tmap_k32 / tmap_v64 unused); invalid indices leave zero rows and are masked through
+// validity bits.
 template <bool F16, bool PREFILL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PREFILL ? ptc::kPrefillThreads : ptc::kThreads, 1)
 mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtensorMap tmap_q,
@@ -226,11 +221,13 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     // nothing was issued; fall through to the common exit
   } else if ((warp == 4 || warp >= 8) && PREFILL) {
     // ================================ Q and K loader, sparse prefill ===================
-    // The CTA's 32 token rows of a block (32 x 1152 bytes) are gathered with 16-byte cp.async copies by three warps
-    // (4, 8, 9): 72 warp instructions per block, 24 per warp, consecutive lanes on consecutive pieces of a row.
-    // A warp keeps only a bounded number of such copies in flight (about 8 bytes per clock at L2 latency), and the
-    // TMA engine gathers rows no faster than ~11 bytes per clock (tile::gather4, one 4-row copy per ~46 clocks),
-    // hence several warps.  Each lane's copies arrive on the landing barrier by hardware (arrive.noinc).
+    // The CTA's 32 token rows of a block (32 x 1152 bytes) are gathered with 16-byte cp.async copies by four warps
+    // (4, 8, 9, 10): 72 warp instructions per block, 18 per warp, consecutive lanes on consecutive pieces of a row.
+    // A warp keeps only a bounded number of such copies in flight: measured at the benchmark shape, three gather
+    // warps gave 751 TFLOP/s, four 955-970, five 956, six 920, eight 930.  The TMA engine (tile::gather4, 4 rows x 64
+    // columns per copy) gathers no faster than ~11 bytes per clock and SM, and mixing the two paths was slower
+    // than either (8 of the 32 rows by TMA: 545 TFLOP/s; 16: 466), because the gathers queue behind the forwarding
+    // copies in the TMA engine.  Each lane's copies arrive on the landing barrier by hardware (arrive.noinc).
     // Nothing else of the block is read from global memory: the value operand of both CTAs is put together from
     // these rows by shared-memory copies (warp 6), which also loads Q: the gather runs ahead into the next query
     // token while the current one drains.  Warp 4 publishes the validity bits of the 64 indices.  An index outside
@@ -238,7 +235,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     int g = 0;
     bool alive = true;
     const int s_kv = P.sp.s_kv;
-    const int gw = warp == 4 ? 0 : warp - 7;                 // 0, 1, 2
+    const int gw = warp == 4 ? 0 : warp - 7;                 // 0..3
     const char* kvb = reinterpret_cast<const char*>(P.sp.kv);
     const int64_t row_bytes = P.sp.kv_stride_s * 2;
     for (int wi = 0; wi < tile.n_work && alive; ++wi) {
@@ -272,23 +269,23 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         if (!alive) break;
         if (warp == 4 && lane == 0) FMLA_PTRACE_AT(g, 0);
         const uint32_t dst = sK + st * kKStageBytes;
-#ifndef FMLA_EXP_NO_GATHER     // timing experiment only: results are wrong
-#pragma unroll 8
-        for (int it = 0; it < 24; ++it) {
-          const int e = (gw * 24 + it) * 32 + lane;              // piece e of 32 rows x 72 pieces of 16 bytes
-          const int row = e / 72, piece = e - row * 72;
-          const int idx = __shfl_sync(0xffffffffu, mine, row);
-          const bool ok = idx >= 0;
-          const char* src = kvb + (ok ? (int64_t)idx * row_bytes + piece * 16 : 0);
-          cp_async16(dst + (piece >> 3) * kKChunkBytes + row * 128 + (((piece & 7) ^ (row & 7)) << 4), src, ok);
-        }
-#endif
-        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar(K_LAND0 + st)) : "memory");
         if (warp == 4 && lane == 0) {
           sValid[(g % 6) * 2] = b0;
           sValid[(g % 6) * 2 + 1] = b1;
           tc::mbar_arrive(bar(K_LAND0 + st));
         }
+        constexpr int kInstr = 32 * 72 / 32;                      // warp instructions per block, dealt out round robin
+#pragma unroll
+        for (int inst = 0; inst < kInstr; inst += kGatherWarps) {
+          if (inst + gw >= kInstr) break;
+          const int e = (inst + gw) * 32 + lane;                 // piece e of 32 rows x 72 pieces of 16 bytes
+          const int row = e / 72, piece = e % 72;
+          const int idx = __shfl_sync(0xffffffffu, mine, row);
+          const bool ok = idx >= 0;
+          const char* src = kvb + (ok ? (int64_t)idx * row_bytes + piece * 16 : 0);
+          cp_async16(dst + (piece >> 3) * kKChunkBytes + row * 128 + (((piece & 7) ^ (row & 7)) << 4), src, ok);
+        }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar(K_LAND0 + st)) : "memory");
       }
     }
   } else if (warp == 4) {
@@ -889,27 +886,14 @@ static bool pair_map_4d(CUtensorMap* m, const void* base, uint64_t d1, uint64_t 
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// kv [s_kv][576] (row stride in elements) as a 2-D map for row gathers: box = 64 columns x 1 row
-static bool pair_gather_map(CUtensorMap* m, const void* base, uint64_t rows, int64_t row_stride) {
-  EncodeTiledFn enc = pair_encode_fn();
-  if (!enc) return false;
-  cuuint64_t dims[2] = {576, rows};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride) * 2};
-  cuuint32_t box[2] = {64, 1};
-  cuuint32_t estr[2] = {1, 1};
-  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 bool sparse_prefill_pair_applies(const SparsePrefillKernelParams& sp) { return sp.h_q == 128; }
 
 cudaError_t launch_sparse_prefill_pair(const SparsePrefillKernelParams& sp, cudaStream_t stream) {
   TcParams P = {};
   P.sp = sp;
-  CUtensorMap tq, tg;
+  CUtensorMap tq;
   // q [s_q][h_q][576] as (col, head, token, 1)
   if (!pair_map_4d(&tq, sp.q, sp.h_q, sp.s_q, 1, sp.q_stride_h, sp.q_stride_s, sp.q_stride_s * sp.s_q, 64, 1)) return cudaErrorInvalidValue;
-  if (!pair_gather_map(&tg, sp.kv, sp.s_kv, sp.kv_stride_s)) return cudaErrorInvalidValue;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
   const int lanes = max(1, min(sp.s_q, sms / 2));
@@ -920,7 +904,7 @@ cudaError_t launch_sparse_prefill_pair(const SparsePrefillKernelParams& sp, cuda
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  kern<<<dim3(2, lanes, 1), ptc::kPrefillThreads, ptc::SMEM_BYTES, stream>>>(P, tq, tg, tg);
+  kern<<<dim3(2, lanes, 1), ptc::kPrefillThreads, ptc::SMEM_BYTES, stream>>>(P, tq, tq, tq);    // the K / V maps are not used in this mode
   return cudaGetLastError();
 }
 
