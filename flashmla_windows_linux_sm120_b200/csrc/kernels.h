@@ -107,6 +107,8 @@ bool decode_dense_merges_in_kernel(const DecodeKernelParams& p);
 cudaError_t launch_decode_dense_pair(const DecodeKernelParams& p, cudaStream_t stream);
 cudaError_t read_decode_pair_status(int* host_status, bool reset);
 // sparse prefill forward as CTA pairs with TMA row gathers (mla_pair.cu); used by launch_sparse_prefill_tc for 128 heads
+bool decode_sparse_pair_applies(const DecodeKernelParams& p);
+cudaError_t launch_decode_sparse_pair(const DecodeKernelParams& p, cudaStream_t stream);
 bool sparse_prefill_pair_applies(const SparsePrefillKernelParams& sp);
 cudaError_t launch_sparse_prefill_pair(const SparsePrefillKernelParams& sp, cudaStream_t stream);
 // Merge of split partials for a decode call (reads num_splits; skips unsplit requests).

@@ -41,6 +41,7 @@
 #include "tc_common.cuh"
 
 #include <cuda.h>
+#include <cuda_fp8.h>
 
 #include <cstdlib>
 
@@ -80,6 +81,11 @@ constexpr int kThreads = 256;
 #endif
 constexpr int kGatherWarps = FMLA_GATHER_WARPS;                 // sparse prefill: warp 4 and warps 8 .. 6 + kGatherWarps
 constexpr int kPrefillThreads = (7 + kGatherWarps) * 32;
+#ifndef FMLA_DECODE_GROUPS
+#define FMLA_DECODE_GROUPS 2
+#endif
+constexpr int kDecodeGatherGroups = FMLA_DECODE_GROUPS;            // sparse FP8 decode: groups of four gather warps that take alternate blocks
+constexpr int kSparseDecodeThreads = (7 + 4 * kDecodeGatherGroups) * 32;
 }  // namespace ptc
 
 __device__ int g_decode_pair_status = 0;
@@ -149,16 +155,19 @@ __device__ __forceinline__ void pv_block_pair(uint32_t tmem_o, uint64_t desc_p_s
 }
 
 // Decode: grid (s_q * hq_per_hk / 64, h_k, parts), clusters of two CTAs along x; 256 threads.
-// PREFILL (sparse prefill forward, 128 heads): grid (2, lanes), every pair walks the query tokens lane, lane + lanes, ..;
+// kSparseDecode (FP8 cache, 128 heads): grid (2, s_q, parts); token rows gathered by index and de-quantised by two
+// groups of four warps (480 threads), everything else as in the prefill mode below, outputs as in the dense mode.
+// kSparsePrefill (sparse prefill forward, 128 heads): grid (2, lanes), every pair walks the query tokens lane, lane + lanes, ..;
 // each CTA gathers its 32 token rows of a 64-index block from kv[s_kv, 576] with cp.async and the value operand is
 // forwarded from those rows (tmap_k32 / tmap_v64 unused); invalid indices leave zero rows and are masked through
 // validity bits.
-template <bool F16, bool PREFILL>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PREFILL ? ptc::kPrefillThreads : ptc::kThreads, 1)
+template <bool F16, int WM>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(WM == kDense ? ptc::kThreads : WM == kSparsePrefill ? ptc::kPrefillThreads : ptc::kSparseDecodeThreads, 1)
 mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_k32, const __grid_constant__ CUtensorMap tmap_v64) {
   using namespace ptc;
-  constexpr int WM = PREFILL ? kSparsePrefill : kDense;
+  constexpr bool PREFILL = WM == kSparsePrefill;     // output / scale / work list of the prefill interface
+  constexpr bool SPARSE = WM != kDense;              // token rows gathered by index, value operand forwarded from them
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t sbase = smem_u32(smem);
   const uint32_t sQ = sbase + Q_OFF, sK = sbase + K_OFF, sV = sbase + V_OFF, sP = sbase + P_OFF;
@@ -202,9 +211,9 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     // prefill: a K stage is free again once its S has completed (one commit) and the value columns forwarded out of
     // it have landed in both CTAs (one arrival from the V relay of each CTA)
     // and a K stage has landed when every lane of the gather warps has arrived by hardware, plus the thread that
-    // published the validity bits
+    // published the validity bits (prefill), or when every gather warp has stored its rows (FP8 decode)
     for (int i = Q_EMPTY; i < NUM_BARS; ++i)
-      tc::mbar_init(bar(i), !PREFILL ? 1 : (i >= K_EMPTY0 && i <= K_EMPTY2) ? 3 : (i >= K_LAND0 && i <= K_LAND2) ? kGatherWarps * 32 + 1 : 1);
+      tc::mbar_init(bar(i), !SPARSE ? 1 : (i >= K_EMPTY0 && i <= K_EMPTY2) ? 3 : (i >= K_LAND0 && i <= K_LAND2) ? (PREFILL ? kGatherWarps * 32 + 1 : kGatherWarps) : 1);
     tc::fence_mbar_init();
     *sAbort = 0;
     if (misaligned) tc::report_status(status, 30);
@@ -219,7 +228,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
 
   if (misaligned) {
     // nothing was issued; fall through to the common exit
-  } else if ((warp == 4 || warp >= 8) && PREFILL) {
+  } else if ((warp == 4 || warp >= 8) && WM == kSparsePrefill) {
     // ================================ Q and K loader, sparse prefill ===================
     // The CTA's 32 token rows of a block (32 x 1152 bytes) are gathered with 16-byte cp.async copies by four warps
     // (4, 8, 9, 10): 72 warp instructions per block, 18 per warp, consecutive lanes on consecutive pieces of a row.
@@ -288,6 +297,131 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar(K_LAND0 + st)) : "memory");
       }
     }
+  } else if ((warp == 4 || warp >= 8) && WM == kSparseDecode) {
+    // ================================ K loader, sparse FP8 decode ======================
+    // Groups of four gather warps, eight of the CTA's 32 token rows per warp.  For one 656-byte record the 32 lanes read the 32
+    // 16-byte pieces of e4m3 values (512 contiguous bytes), their tile's scale, and 8 lanes the bf16 rope part;
+    // bf16(fp32(e4m3) * scale) goes into the K stage in the layout TMA would produce.  Every record is de-quantised
+    // once per pair: the value operand of both CTAs is forwarded from these rows (warp 6).  The raw bytes of the
+    // next block are fetched into registers before the wait for the stage, across requests.  Warp 4 also
+    // publishes the validity bits of all 64 indices of a block.
+    const int gi = warp == 4 ? 0 : warp - 7;                 // gather warp 0 .. 4 * kDecodeGatherGroups - 1
+    const int gw = gi & 3, grp = gi >> 2;                    // rows 8*gw .. of the blocks grp, grp + groups, ..
+    const bool publisher = gw == 0;                          // this warp also publishes the validity bits of its blocks
+    const unsigned char* cache = reinterpret_cast<const unsigned char*>(p.kcache);
+    uint4 nope[8], rope[8];
+    float scl[8];
+    auto to_slot = [&](int v, int batch) {
+      if (p.indices_logical) {       // token position of the request -> physical slot through its block table
+        const int pos = v;
+        v = -1;
+        if (pos >= 0 && pos < __ldg(p.seqlens_k + batch)) v = __ldg(p.block_table + batch * p.block_table_stride_b + (pos >> 6)) * 64 + (pos & 63);
+      }
+      return (v < 0 || v >= p.num_blocks * 64) ? -1 : v;
+    };
+    // Within a group the index reader runs two of its blocks ahead of the stores and the record reader one: the
+    // index -> record chain of loads would otherwise be paid, end to end, once per block.  The groups take
+    // alternate blocks, so that the record reads of consecutive blocks are in flight together.
+    int c_wi = 0, c_blk = 0;         // position of the index reader in the CTA's block list
+    Work c_r = get_work<WM>(P, tile, 0);
+    while (c_wi < tile.n_work && c_r.blk_hi == c_r.blk_lo) { ++c_wi; if (c_wi < tile.n_work) c_r = get_work<WM>(P, tile, c_wi); }
+    c_blk = c_r.blk_lo;
+    auto advance = [&] {
+      if (c_wi >= tile.n_work) return;
+      ++c_blk;
+      while (c_wi < tile.n_work && c_blk >= c_r.blk_hi) {
+        ++c_wi;
+        if (c_wi < tile.n_work) { c_r = get_work<WM>(P, tile, c_wi); c_blk = c_r.blk_lo; }
+      }
+    };
+    for (int i = 0; i < grp; ++i) advance();
+    // Raw index words of the group's next unread block, and the request they belong to: lanes 0..7 the row
+    // 8*gw + lane of this CTA's part; publisher: tokens lane and 32 + lane.  The words are only looked at one turn
+    // later (an instruction that consumes a load waits for it, in program order).
+    struct Raw { int mine, t0, t1, batch; };
+    auto read_indices = [&](Raw& w) -> bool {
+      if (c_wi >= tile.n_work) return false;
+      w.mine = __ldg(c_r.idx + c_blk * 64 + 32 * static_cast<int>(rank) + gw * 8 + (lane & 7));
+      if (publisher) {
+        w.t0 = __ldg(c_r.idx + c_blk * 64 + lane);
+        w.t1 = __ldg(c_r.idx + c_blk * 64 + 32 + lane);
+      }
+      w.batch = c_r.batch;
+      for (int i = 0; i < kDecodeGatherGroups; ++i) advance();
+      return true;
+    };
+    auto read_records = [&](int my_slot) {
+#pragma unroll
+      for (int rr = 0; rr < 8; ++rr) {
+        const int slot = __shfl_sync(0xffffffffu, my_slot, rr);
+        nope[rr] = make_uint4(0, 0, 0, 0);
+        rope[rr] = make_uint4(0, 0, 0, 0);
+        scl[rr] = 0.f;
+        if (slot >= 0) {
+          const unsigned char* rec = cache + (int64_t)(slot >> 6) * p.k_stride_block + (slot & 63) * p.k_stride_row;
+          nope[rr] = __ldg(reinterpret_cast<const uint4*>(rec) + lane);
+          scl[rr] = __ldg(reinterpret_cast<const float*>(rec + 512) + (lane >> 3));
+          if (lane < 8) rope[rr] = __ldg(reinterpret_cast<const uint4*>(rec + 528) + lane);
+        }
+      }
+    };
+    // byte offset of 16-byte piece `piece` (0..71) of row `row` (0..31) in a K stage: 4 KB chunks of 64 columns, 128-byte swizzle
+    auto stage_off = [](int row, int piece) { return (piece >> 3) * kKChunkBytes + row * 128 + (((piece & 7) ^ (row & 7)) << 4); };
+    int g = grp;
+    bool alive = true;
+    uint32_t b0 = 0, b1 = 0;
+    Raw raw = {-1, -1, -1, 0};
+    auto use_indices = [&] {       // validity bits and record reads of the block whose index words are in `raw`
+      if (publisher) {
+        b0 = __ballot_sync(0xffffffffu, to_slot(raw.t0, raw.batch) >= 0);
+        b1 = __ballot_sync(0xffffffffu, to_slot(raw.t1, raw.batch) >= 0);
+      }
+      read_records(to_slot(raw.mine, raw.batch));
+    };
+    bool have = read_indices(raw);
+    if (have) use_indices();
+    bool have_n = have && read_indices(raw);
+    while (have && alive) {
+      const int st = g % kKStages;
+      alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(K_EMPTY0 + st), ((g / kKStages) & 1) ^ 1, status, 102));
+      if (!alive) break;
+      if (publisher && lane == 0) FMLA_PTRACE_AT(g, 0);
+      const uint32_t stage = sK + st * kKStageBytes;
+#pragma unroll
+      for (int rr = 0; rr < 8; ++rr) {
+        const int row = gw * 8 + rr;
+        const float scale = scl[rr];
+        const uint32_t w[4] = {nope[rr].x, nope[rr].y, nope[rr].z, nope[rr].w};
+        uint32_t o[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          // 4 e4m3 bytes -> 4 floats (exact), * scale in fp32, round to bf16
+          const __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w[k] & 0xffffu), __NV_E4M3);
+          const __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w[k] >> 16), __NV_E4M3);
+          const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&h01));
+          const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
+          o[k * 2] = pack_bf16x2(f01.x * scale, f01.y * scale);
+          o[k * 2 + 1] = pack_bf16x2(f23.x * scale, f23.y * scale);
+        }
+        pst_shared_v4(stage + stage_off(row, lane * 2), make_uint4(o[0], o[1], o[2], o[3]));
+        pst_shared_v4(stage + stage_off(row, lane * 2 + 1), make_uint4(o[4], o[5], o[6], o[7]));
+        if (lane < 8) pst_shared_v4(stage + stage_off(row, 64 + lane), rope[rr]);
+      }
+      if (publisher && lane == 0) {
+        sValid[(g % 6) * 2] = b0;
+        sValid[(g % 6) * 2 + 1] = b1;
+      }
+      tc::fence_proxy_async_smem();      // these stores -> the forwarding copies and the tensor pipe
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(bar(K_LAND0 + st));
+      g += kDecodeGatherGroups;
+      // the records of the next block (its indices are here already), then the indices of the one after
+      have = have_n;
+      if (have) {
+        use_indices();
+        have_n = read_indices(raw);
+      }
+    }
   } else if (warp == 4) {
     // ================================ Q and K loader ===================================
     if (tc::elect_one()) {
@@ -345,7 +479,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         ++req;
       }
     }
-  } else if (warp == 6 && PREFILL) {
+  } else if (warp == 6 && SPARSE) {
     // ================================ K relay and V forwarder, sparse prefill ==========
     // The gathered rows of this CTA (32 tokens x 576 columns) hold the value columns of those tokens for both CTAs.
     // Once they have landed, each 64-column chunk of the value part goes, as one 4 KB shared-memory copy, to the
@@ -371,7 +505,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
 #pragma unroll
           for (int c = 0; c < 9; ++c)
             tc::tma_load_4d(c < kQTmemChunks ? sV + c * kChunkBytes : sQ + (c - kQTmemChunks) * kChunkBytes, &tmap_q, c * 64, tile.head0,
-                            r.batch, 0, q_bar);
+                            PREFILL ? r.batch : tile.sq, PREFILL ? 0 : r.batch, q_bar);
         }
         alive = tc::mbar_wait(bar(QT_DONE), req & 1, status, 107);       // in both CTAs: the commit goes to both
         ++req;
@@ -446,7 +580,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         const int st = g & 1;
         alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(V_LAND0 + st), (g >> 1) & 1, status, 104));
         if (!alive) break;
-        const int rows_valid = PREFILL ? 64 : r.seqlen - blk * 64;
+        const int rows_valid = SPARSE ? 64 : r.seqlen - blk * 64;
         if (rows_valid < 64) {
           unsigned char* stage = smem + V_OFF + st * kVStageBytes;
           const int nrows = 64 - rows_valid;
@@ -460,7 +594,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         if (lane == 0) {
           FMLA_PTRACE_AT(g, 13);
           tc::mbar_arrive_cluster(lbar(V_FULL0 + st));
-          if constexpr (PREFILL) {      // every copy out of K stage g % 3 of either CTA into this V stage has completed
+          if constexpr (SPARSE) {       // every copy out of K stage g % 3 of either CTA into this V stage has completed
             tc::mbar_arrive_cluster(tc::mapa(bar(K_EMPTY0 + g % kKStages), 0));
             tc::mbar_arrive_cluster(tc::mapa(bar(K_EMPTY0 + g % kKStages), 1));
           }
@@ -477,7 +611,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
       alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_LAND), req & 1, status, 111));
       if (!alive) break;
       if (lane == 0) tc::mbar_arrive_cluster(lbar(Q_FULL));
-      for (int blk = r.blk_lo; blk < r.blk_hi && alive && !PREFILL; ++blk, ++g) {     // prefill: warp 6 relays K
+      for (int blk = r.blk_lo; blk < r.blk_hi && alive && !SPARSE; ++blk, ++g) {      // sparse modes: warp 6 relays K
         const int st = g % kKStages;
         alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(K_LAND0 + st), (g / kKStages) & 1, status, 112));
         if (alive && lane == 0) tc::mbar_arrive_cluster(lbar(K_FULL0 + st));
@@ -490,7 +624,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
       constexpr uint32_t idesc_s = tc::idesc_bf16_f32(128, 64, 0, 0, F16);
       constexpr uint32_t idesc_o = tc::idesc_bf16_f32(128, 256, 0, 1, F16);
       const uint64_t desc_q = tc::smem_desc_sw128(sQ, 16, 1024);             // A of S, chunks 6..8: K-major
-      const uint64_t desc_qstage = tc::smem_desc_sw128(PREFILL ? sV : sK, 16, 1024);   // chunks 0..5 of Q where the loader stages them
+      const uint64_t desc_qstage = tc::smem_desc_sw128(SPARSE ? sV : sK, 16, 1024);    // chunks 0..5 of Q where the loader stages them
       const uint64_t desc_k = tc::smem_desc_sw128(sK, 16, 1024);             // B of S: K-major, 32 rows per CTA (stage 0)
       const uint64_t desc_p = tc::smem_desc_sw128(sP, 16, 1024);             // A of PV: K-major
       const uint64_t desc_v = tc::smem_desc_sw128(sV, kChunkBytes, 1024);    // B of PV: MN-major, 64-wide column groups 8 KB apart
@@ -571,7 +705,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
             after_issue = 2;
 #endif
           } else if (js < nblk && (m & 0x18u) == 0x18u) {
-            if constexpr (PREFILL) tc::fence_proxy_async_smem();   // K rows came through cp.async
+            if constexpr (SPARSE) tc::fence_proxy_async_smem();    // K rows came through cp.async / plain stores
             tc::tc_fence_after();
             if (lane == 0) { FMLA_PTRACE_AT(gs, 2); FMLA_GTRACE_AT(gs, 0, 3); }
             if (tc::elect_one()) {
@@ -636,7 +770,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         tc::mbar_arrive_cluster(l_s_empty0 + st * 8);
         if (tid == 0) { FMLA_PTRACE_AT(g, 7); FMLA_GTRACE_AT(g, rank, 1); }
 
-        if constexpr (PREFILL) {
+        if constexpr (SPARSE) {
           vbits = sValid[(g % 6) * 2 + th];
         } else {
           const int tok0 = (r.blk_lo + j) * 64 + th * 32;
@@ -886,6 +1020,25 @@ static bool pair_map_4d(CUtensorMap* m, const void* base, uint64_t d1, uint64_t 
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+bool decode_sparse_pair_applies(const DecodeKernelParams& p) { return p.h_k == 1 && p.hq_per_hk == 128 && !p.is_f16; }
+
+cudaError_t launch_decode_sparse_pair(const DecodeKernelParams& p, cudaStream_t stream) {
+  TcParams P = {};
+  P.d = p;
+  CUtensorMap tq;
+  // q [b][s_q][h_q][576] ; box = 64 heads x 64 columns
+  if (!pair_map_4d(&tq, p.q, p.h_q, p.s_q, p.b, p.q_stride_h, p.q_stride_s, p.q_stride_b, 64, 1)) return cudaErrorInvalidValue;
+  auto kern = mla_pair_kernel<false, kSparseDecode>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ptc::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  kern<<<dim3(2, p.s_q, p.num_sm_parts), ptc::kSparseDecodeThreads, ptc::SMEM_BYTES, stream>>>(P, tq, tq, tq);   // the K / V maps are not used in this mode
+  return cudaGetLastError();
+}
+
 bool sparse_prefill_pair_applies(const SparsePrefillKernelParams& sp) { return sp.h_q == 128; }
 
 cudaError_t launch_sparse_prefill_pair(const SparsePrefillKernelParams& sp, cudaStream_t stream) {
@@ -897,7 +1050,7 @@ cudaError_t launch_sparse_prefill_pair(const SparsePrefillKernelParams& sp, cuda
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
   const int lanes = max(1, min(sp.s_q, sms / 2));
-  auto kern = mla_pair_kernel<false, true>;
+  auto kern = mla_pair_kernel<false, kSparsePrefill>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ptc::SMEM_BYTES);
@@ -928,7 +1081,7 @@ cudaError_t launch_decode_dense_pair(const DecodeKernelParams& p, cudaStream_t s
   const dim3 grid(p.s_q * n_hb, p.h_k, p.num_sm_parts);
   static bool attr_set[2] = {false, false};      // idempotent, so a race between threads is harmless
   if (p.is_f16) {
-    auto kern = mla_pair_kernel<true, false>;
+    auto kern = mla_pair_kernel<true, kDense>;
     if (!attr_set[1]) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ptc::SMEM_BYTES);
       if (e != cudaSuccess) return e;
@@ -936,7 +1089,7 @@ cudaError_t launch_decode_dense_pair(const DecodeKernelParams& p, cudaStream_t s
     }
     kern<<<grid, ptc::kThreads, ptc::SMEM_BYTES, stream>>>(P, tq, tk, tv);
   } else {
-    auto kern = mla_pair_kernel<false, false>;
+    auto kern = mla_pair_kernel<false, kDense>;
     if (!attr_set[0]) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ptc::SMEM_BYTES);
       if (e != cudaSuccess) return e;

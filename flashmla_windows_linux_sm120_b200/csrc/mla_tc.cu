@@ -722,6 +722,7 @@ cudaError_t launch_decode_dense_tc(const DecodeKernelParams& p, cudaStream_t str
 }
 
 cudaError_t launch_decode_sparse_tc(const DecodeKernelParams& p, cudaStream_t stream) {
+  if (decode_sparse_pair_applies(p) && pair_kernel_enabled()) return launch_decode_sparse_pair(p, stream);
   TcParams P = {};
   P.d = p;
   CUtensorMap tq;
