@@ -816,6 +816,7 @@ class Runner:
     def __init__(self, device, local, rank, world, seed):
         self.device, self.local, self.rank, self.world, self.seed = device, local, rank, world, seed
         self.stream = torch.cuda.current_stream()
+        self.sustained = True
         if world > 1:
             import torch.distributed as dist
             self.dist = dist
@@ -934,7 +935,7 @@ class Runner:
             r["nccl_all_gather_baseline_ms"] = ms_n
             r["peer_merge_ms"] = ms
         # sustained: the same step for at least a second
-        if headline:
+        if headline and self.sustained:
             t0 = time.perf_counter()
             n, tot = 0, 0.0
             sampler = ClockSampler(self.local).start()
@@ -994,6 +995,7 @@ def main():
     ap.add_argument("--small", action="store_true", help="shrink the workload (profiler captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="do not run the other workloads after the default one")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the one-second sustained stretch (profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     wl = make_workload(args.workload, args.small)
@@ -1012,6 +1014,7 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     runner = Runner(device, local, rank, world, args.seed)
+    runner.sustained = not args.no_sustained
     head = runner.measure(wl, args.steps, args.warmup, headline=True, do_cpu=not args.no_cpu_baseline and world == 1)
     wl.release()
 

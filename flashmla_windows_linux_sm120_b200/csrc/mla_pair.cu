@@ -410,7 +410,9 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
       if (publisher && lane == 0) {
         sValid[(g % 6) * 2] = b0;
         sValid[(g % 6) * 2 + 1] = b1;
+        FMLA_PTRACE_AT(g, 1);
       }
+      if (gw == 3 && lane == 0) FMLA_PTRACE_AT(g, 10);
       tc::fence_proxy_async_smem();      // these stores -> the forwarding copies and the tensor pipe
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(bar(K_LAND0 + st));
@@ -489,55 +491,97 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     // Q of a query token: chunks 6..8 go to their place, chunks 0..5 are staged in the V ring (48 of its 64 KB) until
     // the leader has copied them into tensor memory.  Loaded once every S of the previous token has completed (Q in
     // shared and tensor memory free) and its last two P V have released the V stages.
+    // One thread does all of it without ever blocking on one condition while another could be served: the relay of
+    // a landed K stage to the leader (the next S must not wait behind a V stage that is still in use), the Q load
+    // of the next request, the forwarding copies.
     if (tc::elect_one()) {
       tc::prefetch_tensormap(&tmap_q);
-      int g = 0, req = 0;
-      bool alive = true;
-      for (int wi = 0; wi < tile.n_work && alive; ++wi) {
+      int total = 0;
+      for (int wi = 0; wi < tile.n_work; ++wi) {
         const Work r = get_work<WM>(P, tile, wi);
-        if (r.blk_hi == r.blk_lo) continue;
-        alive = tc::mbar_wait(bar(Q_EMPTY), (req & 1) ^ 1, status, 101);
-        for (int gg = max(0, g - 2); gg < g && alive; ++gg) alive = tc::mbar_wait(bar(V_EMPTY0 + (gg & 1)), (gg >> 1) & 1, status, 103);
-        if (!alive) break;
-        {
-          const uint32_t q_bar = rank == 0 ? bar(Q_FULL) : bar(Q_LAND);
-          tc::mbar_arrive_expect_tx(q_bar, kQBytes);
-#pragma unroll
-          for (int c = 0; c < 9; ++c)
-            tc::tma_load_4d(c < kQTmemChunks ? sV + c * kChunkBytes : sQ + (c - kQTmemChunks) * kChunkBytes, &tmap_q, c * 64, tile.head0,
-                            PREFILL ? r.batch : tile.sq, PREFILL ? 0 : r.batch, q_bar);
+        total += max(r.blk_hi - r.blk_lo, 0);
+      }
+      int kg = 0;                       // next block whose landing is relayed
+      int vg = 0, v_end = 0, req = 0;   // next block to forward, end of the current request's blocks, requests started
+      int wi = 0;
+      Work r = get_work<WM>(P, tile, 0);
+      auto skip_empty = [&] {
+        while (wi < tile.n_work && r.blk_hi <= r.blk_lo) { ++wi; if (wi < tile.n_work) r = get_work<WM>(P, tile, wi); }
+        if (wi < tile.n_work) v_end = vg + (r.blk_hi - r.blk_lo);
+      };
+      skip_empty();
+      enum { kNeedQ, kWaitQt, kForward };
+      int state = kNeedQ, idle = 0;
+      bool alive = true;
+      auto v_empty_after = [&](int gg) { return tc::mbar_test_wait(bar(V_EMPTY0 + (gg & 1)), (gg >> 1) & 1); };   // P V of block gg has completed
+      while (alive && (kg < total || wi < tile.n_work)) {
+        bool did = false;
+        if (kg < total && tc::mbar_test_wait(bar(K_LAND0 + kg % kKStages), (kg / kKStages) & 1)) {
+          tc::fence_proxy_async_smem();        // rows written by cp.async / plain stores -> bulk copies and the tensor pipe
+          tc::mbar_arrive_cluster(lbar(K_FULL0 + kg % kKStages));
+          FMLA_PTRACE_AT(kg, 15);
+          ++kg;
+          did = true;
         }
-        alive = tc::mbar_wait(bar(QT_DONE), req & 1, status, 107);       // in both CTAs: the commit goes to both
-        ++req;
-        for (int blk = r.blk_lo; blk < r.blk_hi && alive; ++blk, ++g) {
-          const int kst = g % kKStages, vst = g & 1;
-          alive = tc::mbar_wait(bar(K_LAND0 + kst), (g / kKStages) & 1, status, 112);
-          if (!alive) break;
-          tc::fence_proxy_async_smem();        // rows written by cp.async -> bulk copies and the tensor pipe
-          tc::mbar_arrive_cluster(lbar(K_FULL0 + kst));
-          // P V of block g-2 has completed in both CTAs (its commit goes to both): both V stages are free
-          alive = tc::mbar_wait(bar(V_EMPTY0 + vst), ((g >> 1) & 1) ^ 1, status, 103);
-          if (!alive) break;
-          FMLA_PTRACE_AT(g, 12);
+        if (wi < tile.n_work) {
+          if (state == kNeedQ) {
+            // every S of the previous request has completed (Q in shared and tensor memory free) and its last two
+            // P V have released the V stages the new Q is staged in
+            if (tc::mbar_test_wait(bar(Q_EMPTY), (req & 1) ^ 1) && (vg < 1 || v_empty_after(vg - 1)) && (vg < 2 || v_empty_after(vg - 2))) {
+              const uint32_t q_bar = rank == 0 ? bar(Q_FULL) : bar(Q_LAND);
+              tc::mbar_arrive_expect_tx(q_bar, kQBytes);
+#pragma unroll
+              for (int c = 0; c < 9; ++c)
+                tc::tma_load_4d(c < kQTmemChunks ? sV + c * kChunkBytes : sQ + (c - kQTmemChunks) * kChunkBytes, &tmap_q, c * 64, tile.head0,
+                                PREFILL ? r.batch : tile.sq, PREFILL ? 0 : r.batch, q_bar);
+              state = kWaitQt;
+              did = true;
+            }
+          } else if (state == kWaitQt) {
+            if (tc::mbar_test_wait(bar(QT_DONE), req & 1)) {       // in both CTAs: the commit goes to both
+              ++req;
+              state = kForward;
+              did = true;
+            }
+          } else if (vg < kg && (vg < 2 || v_empty_after(vg - 2))) {
+            // the rows of block vg have landed (and were fenced above); P V of block vg-2 has completed in both CTAs
+            // (its commit goes to both): both V stages are free
+            const int kst = vg % kKStages, vst = vg & 1;
+            FMLA_PTRACE_AT(vg, 12);
 #ifdef FMLA_EXP_NO_FWD          // timing experiment only: results are wrong
-          tc::mbar_arrive(bar(V_LAND0 + vst));
-          continue;
+            tc::mbar_arrive(bar(V_LAND0 + vst));
+#else
+            tc::mbar_arrive_expect_tx(bar(V_LAND0 + vst), kVStageBytes);      // 16 KB from this CTA, 16 KB from the peer
+#pragma unroll
+            for (int d = 0; d < 2; ++d) {
+              const uint32_t dest = rank ^ static_cast<uint32_t>(d);
+              const uint32_t dst_bar = tc::mapa(bar(V_LAND0 + vst), dest);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int chunk = (i >> 1) * 4 + 2 * static_cast<int>(dest) + (i & 1);     // value columns 64*chunk ..
+                const uint32_t src = sK + kst * kKStageBytes + chunk * kKChunkBytes;
+                const uint32_t dst = tc::mapa(sV + vst * kVStageBytes + i * kChunkBytes + rank * kKChunkBytes, dest);
+                asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+                             "r"(src), "r"(kKChunkBytes), "r"(dst_bar)
+                             : "memory");
+              }
+            }
 #endif
-          tc::mbar_arrive_expect_tx(bar(V_LAND0 + vst), kVStageBytes);      // 16 KB from this CTA, 16 KB from the peer
-#pragma unroll
-          for (int d = 0; d < 2; ++d) {
-            const uint32_t dest = rank ^ static_cast<uint32_t>(d);
-            const uint32_t dst_bar = tc::mapa(bar(V_LAND0 + vst), dest);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int chunk = (i >> 1) * 4 + 2 * static_cast<int>(dest) + (i & 1);     // value columns 64*chunk ..
-              const uint32_t src = sK + kst * kKStageBytes + chunk * kKChunkBytes;
-              const uint32_t dst = tc::mapa(sV + vst * kVStageBytes + i * kChunkBytes + rank * kKChunkBytes, dest);
-              asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
-                           "r"(src), "r"(kKChunkBytes), "r"(dst_bar)
-                           : "memory");
+            ++vg;
+            did = true;
+            if (vg == v_end) {
+              ++wi;
+              if (wi < tile.n_work) r = get_work<WM>(P, tile, wi);
+              skip_empty();
+              state = kNeedQ;
             }
           }
+        }
+        if (did) {
+          idle = 0;
+        } else if (++idle > tc::kSpinLimit) {
+          tc::report_status(status, 112);
+          alive = false;
         }
       }
     }
@@ -628,7 +672,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
       const uint64_t desc_k = tc::smem_desc_sw128(sK, 16, 1024);             // B of S: K-major, 32 rows per CTA (stage 0)
       const uint64_t desc_p = tc::smem_desc_sw128(sP, 16, 1024);             // A of PV: K-major
       const uint64_t desc_v = tc::smem_desc_sw128(sV, kChunkBytes, 1024);    // B of PV: MN-major, 64-wide column groups 8 KB apart
-      // every commit goes to the barrier copy of each CTA (two plain commits, no multicast)
+      // every commit goes to the barrier copy of each CTA (two plain commits, each naming one barrier)
       auto commit_both = [&](int b) {
         tc::tc_commit_pair(bar(b));
         tc::tc_commit_pair(tc::mapa(bar(b), 1));

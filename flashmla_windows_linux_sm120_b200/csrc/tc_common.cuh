@@ -177,7 +177,7 @@ __device__ __forceinline__ void mma_ws_ss(uint32_t tmem_d, uint64_t da, uint64_t
 // One thread of the leader CTA (cluster rank 0) issues MMAs that run on the tensor cores of both SMs: M = 128
 // means 64 accumulator rows per CTA, the A operand comes from each CTA's own shared memory and the B operand
 // is split along N (first half from the leader's shared memory, second half from its peer's), at the same
-// shared-memory offsets in both CTAs.  No multicast anywhere: a commit or a copy names one barrier of one CTA.
+// shared-memory offsets in both CTAs.  Every commit or copy names one barrier of one CTA (nothing is broadcast to several CTAs).
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
