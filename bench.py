@@ -45,7 +45,14 @@ if ROOT not in sys.path:
 # (summaries under profiles/).  "full" = captured on the full workload; otherwise bytes per unit of a small
 # case, scaled by the units one launch of the benchmark workload processes (traffic grows in proportion).
 TRAFFIC = {
-    "dense_decode": {"per_token": 708.7e6 / 526851, "unit": "cached token", "source": "full-size capture, 1 pass set"},
+    # mla_pair_kernel<decode>: 640.56 MB read + 27.04 MB written in one launch over 526 851 cached tokens
+    "dense_decode": {"per_token": (640556288 + 27036672) / 526851, "unit": "cached token", "source": "full-size capture (3 metrics, 1 pass)"},
+    # mla_pair_kernel<sparse decode>, --small case (16 requests): 27.26 MB read + 0.03 MB written
+    "sparse_decode": {"per_request": (27259648 + 25856) / 16, "unit": "request of 2048 indices", "source": "small case (16 requests), scaled by requests"},
+    # mla_pair_kernel<prefill>, --small case (512 query tokens): 125.76 MB read + 45.35 MB written, of which the
+    # kv tensor (37.7 MB) is read once whatever the number of query tokens
+    "sparse_prefill": {"fixed": 32768 * 1152.0, "per_query_token": (125763840 + 45354240 - 32768 * 1152) / 512, "unit": "query token",
+                       "source": "small case (512 query tokens), scaled by query tokens"},
 }
 
 FALLBACK_HBM_GBS = 6650.0
@@ -332,6 +339,9 @@ class SparseDecode(Workload):
     kernel_name = "mla_tc_kernel<kSparseDecode>"
     launches_per_step = 2
 
+    def traffic(self):
+        return TRAFFIC["sparse_decode"]["per_request"] * self.b if (self.topk, self.h_q) == (2048, 128) else None
+
     def __init__(self, batch: int = 64, topk: int = 2048, seqlen: int = 32768, h_q: int = 128, small: bool = False):
         if small:
             batch = 16
@@ -427,6 +437,10 @@ class SparsePrefill(Workload):
     launches_per_step = 1
     scaling = "strong"
     sharding = "query tokens sharded (kv replicated), no collective"
+
+    def traffic(self):
+        t = TRAFFIC["sparse_prefill"]
+        return t["fixed"] + t["per_query_token"] * self.s_q if (self.s_kv, self.topk, self.h_q) == (32768, 2048, 128) else None
 
     def __init__(self, s_q: int = 4096, s_kv: int = 32768, topk: int = 2048, h_q: int = 128, small: bool = False):
         if small:
