@@ -64,7 +64,6 @@ constexpr int BAR_OFF = P_OFF + 2 * kChunkBytes;
 constexpr int MX_OFF = BAR_OFF + 256;             // float [3][128] exchange
 constexpr int MISC_OFF = MX_OFF + 1536;
 constexpr int SMEM_BYTES = MISC_OFF + 128;
-static_assert(kQTmemChunks * kChunkBytes <= kKStages * kKStageBytes, "Q staging must fit into the K ring");
 static_assert(kQTmemChunks * kChunkBytes <= 2 * kVStageBytes, "Q staging must fit into the V ring (sparse prefill)");
 // leader-side barriers (waited on by the MMA warp of rank 0; arrivals come from both CTAs)
 // and per-CTA barriers (each CTA waits on its own copy; the leader's commits arrive on both copies)
@@ -203,11 +202,13 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     tc::mbar_init(bar(K_FULL2), 2);
     tc::mbar_init(bar(V_FULL0), 2);
     tc::mbar_init(bar(V_FULL1), 2);
-    tc::mbar_init(bar(S_EMPTY0), 256);
-    tc::mbar_init(bar(S_EMPTY1), 256);
-    tc::mbar_init(bar(P_FULL0), 256);
-    tc::mbar_init(bar(P_FULL1), 256);
-    tc::mbar_init(bar(O_EMPTY), 256);
+    // one arrival per softmax warp of either CTA (lane 0, after the warp has synchronised): 128 remote arrivals per
+    // barrier phase took the peer's P ~700 ns to reach the leader
+    tc::mbar_init(bar(S_EMPTY0), 8);
+    tc::mbar_init(bar(S_EMPTY1), 8);
+    tc::mbar_init(bar(P_FULL0), 8);
+    tc::mbar_init(bar(P_FULL1), 8);
+    tc::mbar_init(bar(O_EMPTY), 8);
     // prefill: a K stage is free again once its S has completed (one commit) and the value columns forwarded out of
     // it have landed in both CTAs (one arrival from the V relay of each CTA)
     // and a K stage has landed when every lane of the gather warps has arrived by hardware, plus the thread that
@@ -425,28 +426,16 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
       }
     }
   } else if (warp == 4) {
-    // ================================ Q and K loader ===================================
+    // ================================ K loader =========================================
+    // depends on nothing but the K ring: it runs ahead into the next request while the current one drains (Q is
+    // staged through the V ring and loaded by warp 6)
     if (tc::elect_one()) {
-      tc::prefetch_tensormap(&tmap_q);
       tc::prefetch_tensormap(&tmap_k32);
-      int g = 0, req = 0;
+      int g = 0;
       bool alive = true;
       for (int wi = 0; wi < tile.n_work && alive; ++wi) {
         const Work r = get_work<WM>(P, tile, wi);
         if (r.blk_hi == r.blk_lo) continue;
-        alive = tc::mbar_wait(bar(Q_EMPTY), (req & 1) ^ 1, status, 101);
-        if (!alive) break;
-        // every S of the previous request has completed: its Q (shared and tensor memory) and the whole K ring
-        // are free.  Chunks 0..5 of the new Q are staged at the start of the K ring, chunks 6..8 go to their place.
-        const uint32_t q_bar = rank == 0 ? bar(Q_FULL) : bar(Q_LAND);
-        tc::mbar_arrive_expect_tx(q_bar, kQBytes);
-#pragma unroll
-        for (int c = 0; c < 9; ++c)
-          tc::tma_load_4d(c < kQTmemChunks ? sK + c * kChunkBytes : sQ + (c - kQTmemChunks) * kChunkBytes, &tmap_q, c * 64, tile.head0,
-                          PREFILL ? r.batch : tile.sq, PREFILL ? 0 : r.batch, q_bar);
-        // the K ring may be refilled once the leader has copied the staged chunks into tensor memory
-        alive = tc::mbar_wait(bar(QT_DONE), req & 1, status, 107);
-        if (!alive) break;
         const int* bt = p.block_table + r.batch * p.block_table_stride_b;
         const int pf = p.l2_prefetch_dist;
         // the leader pulls whole pages into L2 `pf` blocks ahead of the loads of both CTAs (the V parts use the
@@ -478,7 +467,6 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
           for (int c = 0; c < 9; ++c)
             tc::tma_load_4d(sK + st * kKStageBytes + c * kKChunkBytes, &tmap_k32, c * 64, tile.kh, 32 * static_cast<int>(rank), page, full);
         }
-        ++req;
       }
     }
   } else if (warp == 6 && SPARSE) {
@@ -587,12 +575,31 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     }
   } else if (warp == 6) {
     // ================================ V loader =========================================
+    // Also loads Q: chunks 6..8 go to their place, chunks 0..5 are staged in the V ring (48 of its 64 KB) until the
+    // leader has copied them into tensor memory -- once every S of the previous request has completed (Q in shared
+    // and tensor memory free) and its last two P V have released the V stages.
     if (tc::elect_one()) {
+      tc::prefetch_tensormap(&tmap_q);
       tc::prefetch_tensormap(&tmap_v64);
-      int g = 0;
+      int g = 0, req = 0;
       bool alive = true;
       for (int wi = 0; wi < tile.n_work && alive; ++wi) {
         const Work r = get_work<WM>(P, tile, wi);
+        if (r.blk_hi == r.blk_lo) continue;
+        alive = tc::mbar_wait(bar(Q_EMPTY), (req & 1) ^ 1, status, 101);
+        for (int gg = max(0, g - 2); gg < g && alive; ++gg) alive = tc::mbar_wait(bar(V_EMPTY0 + (gg & 1)), (gg >> 1) & 1, status, 103);
+        if (!alive) break;
+        {
+          const uint32_t q_bar = rank == 0 ? bar(Q_FULL) : bar(Q_LAND);
+          tc::mbar_arrive_expect_tx(q_bar, kQBytes);
+#pragma unroll
+          for (int c = 0; c < 9; ++c)
+            tc::tma_load_4d(c < kQTmemChunks ? sV + c * kChunkBytes : sQ + (c - kQTmemChunks) * kChunkBytes, &tmap_q, c * 64, tile.head0,
+                            tile.sq, r.batch, q_bar);
+        }
+        alive = tc::mbar_wait(bar(QT_DONE), req & 1, status, 107);       // the V ring may be refilled
+        if (!alive) break;
+        ++req;
         const int* bt = p.block_table + r.batch * p.block_table_stride_b;
         for (int blk = r.blk_lo; blk < r.blk_hi; ++blk, ++g) {
           const int st = g & 1;
@@ -668,7 +675,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
       constexpr uint32_t idesc_s = tc::idesc_bf16_f32(128, 64, 0, 0, F16);
       constexpr uint32_t idesc_o = tc::idesc_bf16_f32(128, 256, 0, 1, F16);
       const uint64_t desc_q = tc::smem_desc_sw128(sQ, 16, 1024);             // A of S, chunks 6..8: K-major
-      const uint64_t desc_qstage = tc::smem_desc_sw128(SPARSE ? sV : sK, 16, 1024);    // chunks 0..5 of Q where the loader stages them
+      const uint64_t desc_qstage = tc::smem_desc_sw128(sV, 16, 1024);                  // chunks 0..5 of Q where the loader stages them (the V ring)
       const uint64_t desc_k = tc::smem_desc_sw128(sK, 16, 1024);             // B of S: K-major, 32 rows per CTA (stage 0)
       const uint64_t desc_p = tc::smem_desc_sw128(sP, 16, 1024);             // A of PV: K-major
       const uint64_t desc_v = tc::smem_desc_sw128(sV, kChunkBytes, 1024);    // B of PV: MN-major, 64-wide column groups 8 KB apart
@@ -811,7 +818,8 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
 #pragma unroll
           for (int i = 0; i < 32; ++i) sv[i] = 0u;
         }
-        tc::mbar_arrive_cluster(l_s_empty0 + st * 8);
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive_cluster(l_s_empty0 + st * 8);
         if (tid == 0) { FMLA_PTRACE_AT(g, 7); FMLA_GTRACE_AT(g, rank, 1); }
 
         if constexpr (SPARSE) {
@@ -884,7 +892,8 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
           pst_shared_v4(sP + st * kChunkBytes + r_row * 128 + ((((th * 4 + q4) ^ (r_row & 7))) << 4),
                         make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]));
         tc::fence_proxy_async_smem();
-        tc::mbar_arrive_cluster(l_p_full0 + st * 8);
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive_cluster(l_p_full0 + st * 8);
         if (tid == 0) { FMLA_PTRACE_AT(g, 11); FMLA_GTRACE_AT(g, rank, 2); }
       }
 
@@ -943,7 +952,8 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
       }
       if (nblk > 0) {
         tc::tc_fence_before();
-        tc::mbar_arrive_cluster(l_o_empty);
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive_cluster(l_o_empty);
         ++req;
       }
       if (tid == 0) FMLA_PTRACE_AT(g - 1, 15);
