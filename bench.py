@@ -2,7 +2,7 @@
 """Benchmark of the MLA attention hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
-                    [--small] [--no-extras] [--no-cpu-baseline]
+                    [--small] [--no-extras] [--no-cpu-baseline] [--no-sustained] [--no-graph]
 
 One "step" = one pass of the hot path (the public API call) over one batch of seeded synthetic input.
 Default workload: dense BF16 MLA decode at the DeepSeek-V3 shape (batch 128 per GPU, s_q 1, 128 heads,
@@ -211,6 +211,8 @@ class Workload:
         return h2d, self._E.d2h
 
     def release(self):
+        self._graph_out = None
+        self._graph = None
         for k in list(self.__dict__):
             if isinstance(self.__dict__[k], (torch.Tensor, list, dict, argparse.Namespace)):
                 del self.__dict__[k]
@@ -222,6 +224,23 @@ class Workload:
     def traffic(self):
         return None
 
+    # Launch-bound steps (a decode step is two kernels of ~0.15 ms) are timed as replays of a CUDA graph that holds
+    # one captured step: the host then issues one call per step whatever the cost of the Python launch path.
+    graphable = False
+
+    def capture(self):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._graph_out = self.step()
+        self._graph = g
+
+    def timed_step(self):
+        """What the timed region runs: a replay of the captured step when there is one, else a plain step."""
+        if getattr(self, "_graph", None) is not None:
+            self._graph.replay()
+            return self._graph_out
+        return self.step()
+
 
 class DenseDecode(Workload):
     """Dense BF16 MLA decode at the DeepSeek-V3 shape."""
@@ -229,6 +248,7 @@ class DenseDecode(Workload):
     bound = "hbm"
     kernel_name = "mla_pair_kernel<decode> (+ decode_combine_kernel)"
     launches_per_step = 2          # split-KV attention + combine
+    graphable = True
     e2e_buffers = 2
     e2e_max_steps = 10 ** 9
 
@@ -292,7 +312,7 @@ class DenseDecode(Workload):
     def parity(self, n_req: int = 16):
         """Outputs of one more step against the CPU oracle on n_req requests spread over the batch."""
         from oracle import decode
-        out, lse = self.step()
+        out, lse = self.timed_step()
         torch.cuda.synchronize()
         sel = sorted(set(int(round(i * (self.b - 1) / max(n_req - 1, 1))) for i in range(min(n_req, self.b))))
         lens = self.lens[sel]
@@ -336,8 +356,9 @@ class SparseDecode(Workload):
     metric, unit, dtype = "sparse_fp8_mla_decode_tflops", "TFLOP/s", "bf16 (fp8 e4m3 cache)"
     bound = "tensor"
     key = "sparse_decode"
-    kernel_name = "mla_tc_kernel<kSparseDecode>"
+    kernel_name = "mla_pair_kernel<sparse decode> (+ decode_combine_kernel)"
     launches_per_step = 2
+    graphable = True
 
     def traffic(self):
         return TRAFFIC["sparse_decode"]["per_request"] * self.b if (self.topk, self.h_q) == (2048, 128) else None
@@ -396,7 +417,7 @@ class SparseDecode(Workload):
     def parity(self, n_req: int = 4):
         """n_req requests: their 2048 records are fetched, de-quantised by the codec oracle and attended on the CPU."""
         from oracle import decode, quant
-        out, lse = self.step()
+        out, lse = self.timed_step()
         torch.cuda.synchronize()
         sel = sorted(set(int(round(i * (self.b - 1) / max(n_req - 1, 1))) for i in range(min(n_req, self.b))))
         e_out = e_lse = 0.0
@@ -831,6 +852,7 @@ class Runner:
         self.device, self.local, self.rank, self.world, self.seed = device, local, rank, world, seed
         self.stream = torch.cuda.current_stream()
         self.sustained = True
+        self.use_graph = True
         if world > 1:
             import torch.distributed as dist
             self.dist = dist
@@ -911,7 +933,25 @@ class Runner:
             r.setdefault("error", "set-up failed on another rank")
             return r
         per_kernel = wl.bound == "hbm" and wl.key.startswith("dense_decode")
-        ms, kern, clocks = self.timed(lambda ev: wl.step(ev) if per_kernel else wl.step(), steps, per_kernel)
+        ms_eager, kern, clocks = self.timed(lambda ev: wl.step(ev) if per_kernel else wl.step(), steps, per_kernel)
+        ms = ms_eager
+        captured = False
+        if wl.graphable and self.use_graph:
+            try:
+                wl.capture()
+                for _ in range(3):
+                    wl.timed_step()
+                torch.cuda.synchronize()
+                captured = True
+            except Exception as e:      # noqa: BLE001
+                wl._graph = None
+                r["graph_capture_error"] = f"{type(e).__name__}: {e}"
+            if self.all_ok(captured):
+                ms, _, clocks = self.timed(lambda ev: wl.timed_step(), steps, False)
+                r["launch"] = "replays of a CUDA graph that holds one captured step (scheduler metadata fixed, as in a serving loop)"
+                r["ms_per_step_eager"] = ms_eager
+            else:
+                wl._graph = None
         nbytes, nflops = self.allsum(float(wl.alg_bytes())), self.allsum(float(wl.alg_flops()))
         gbs, tflops = nbytes / (ms * 1e-3) / 1e9, nflops / (ms * 1e-3) / 1e12
         r.update(value=gbs if wl.unit == "GB/s" else tflops, ms_per_step=ms, gb_per_s=gbs, tflops=tflops, clocks=clocks,
@@ -958,7 +998,7 @@ class Runner:
                 self.barrier()
                 e0.record(self.stream)
                 for _ in range(steps * 5):
-                    wl.step()
+                    wl.timed_step()
                 e1.record(self.stream)
                 self.barrier()
                 tot += self.allmax(e0.elapsed_time(e1))
@@ -1009,6 +1049,7 @@ def main():
     ap.add_argument("--small", action="store_true", help="shrink the workload (profiler captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="do not run the other workloads after the default one")
+    ap.add_argument("--no-graph", action="store_true", help="time plain per-step launches instead of CUDA graph replays")
     ap.add_argument("--no-sustained", action="store_true", help="skip the one-second sustained stretch (profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -1029,6 +1070,7 @@ def main():
 
     runner = Runner(device, local, rank, world, args.seed)
     runner.sustained = not args.no_sustained
+    runner.use_graph = not args.no_graph
     head = runner.measure(wl, args.steps, args.warmup, headline=True, do_cpu=not args.no_cpu_baseline and world == 1)
     wl.release()
 
@@ -1056,9 +1098,12 @@ def main():
                     "tflops": head["tflops"], "gb_per_s": head["gb_per_s"], "roofline": head["roofline"],
                     "cpu_baseline": head.get("cpu_baseline"), "e2e": head.get("e2e"), "parity_checked": head.get("parity_checked"),
                     "sustained": head.get("sustained"), "gpu_launches": head["gpu_launches"], "clocks": head["clocks"]}
-            for k in ("imbalance_max_over_mean", "nccl_all_gather_baseline_ms", "peer_merge_ms", "e2e_error"):
+            for k in ("imbalance_max_over_mean", "nccl_all_gather_baseline_ms", "peer_merge_ms", "e2e_error", "ms_per_step_eager",
+                      "graph_capture_error"):
                 if k in head:
                     line[k] = head[k]
+            if "launch" in head:
+                line["config"]["launch"] = head["launch"]
             if extras:
                 line["workloads"] = extras
             print(json.dumps(line))
