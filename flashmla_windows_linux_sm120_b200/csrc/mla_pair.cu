@@ -1,4 +1,6 @@
-// Dense BF16 / FP16 split-KV MLA decode for sm_100a as a CTA pair (cluster of two CTAs, tcgen05 cta_group::2).
+// MLA attention for 128 heads on sm_100a as a CTA pair (cluster of two CTAs, tcgen05 cta_group::2): dense BF16 /
+// FP16 split-KV decode, sparse FP8 split-KV decode and sparse prefill.  The dense mode is described first; the two
+// gathering modes differ in how the K rows reach shared memory and where the V operand comes from (further down).
 //
 // The pair owns 128 query heads of one (query token, kv head, partition): CTA r of the pair (cluster rank r)
 // owns heads 64r .. 64r+63, i.e. the Q tile, the S tile, the P tile and the O accumulator of those heads.
@@ -15,26 +17,36 @@
 // the CTA's Q tile (tcgen05.cp from shared memory, rows duplicated into both lane halves as an M=64-per-CTA
 // A operand wants them), so only chunks 6..8 (24 KB) stay in shared memory -- that is what makes room for
 // the third K stage -- and the S instructions that take A from tensor memory run at 18 instead of 25 clocks.
-// The six chunks pass through the (then idle) K ring on their way: a request's K loads start once its Q copy
-// into tensor memory has completed.
+// The six chunks pass through the V ring on their way (free between the last P V of a request and the first of
+// the next); the K loads depend on nothing but the K ring and run ahead into the next request.
 //
 //   warps 0-3 softmax : as in mla_tc.cu (TMEM lane = row + 64 * (token >= 32)); arrivals that the issuing
 //                       thread waits for go to the leader's barriers (remote arrive from rank 1)
-//   warp 4   K loader : Q tile, then per 64-token block the CTA's 32 token rows.  The leader's copies complete on
+//   warp 4   K loader : per 64-token block the CTA's 32 token rows.  The leader's copies complete on
 //                       the barrier its MMA warp waits on; the peer's copies complete on a barrier of the peer
 //                       and one thread there passes each completion on with a single remote arrive (letting the
 //                       peer's copies count their bytes on the leader's barrier directly -- cp.async.bulk.tensor
 //                       ... cta_group::2 -- made a 36 KB part take about 3 us to be seen as landed)
 //   warp 5   MMA      : rank 0: issues every MMA; rank 1: the relay of the Q / K completions just described
-//   warp 6   V loader : per block 4 boxes of 64 rows x 64 columns, completing on a local barrier
+//   warp 6   V loader : the Q tile of a request, then per block 4 boxes of 64 rows x 64 columns, completing on a local barrier
 //   warp 7   V relay  : waits for the local V part, clears the rows of the last page that lie beyond the
 //                       sequence (they may hold NaN and 0 * NaN must not reach O), tells the leader
 // TMEM (512 columns per CTA, allocated as a pair): O = [0,256), S[0] = [256,288), S[1] = [288,320), Q chunks
 // 0..5 = [320,512) (32 columns each); O / S layouts as in mla_tc.cu (the 64-row halves of an M=128 pair
 // instruction have the layout of the M=64 .ws form).
 //
+// Gathering modes (sparse FP8 decode: 480 threads, sparse prefill: 352 threads).  Each CTA brings only its 32 token
+// rows of a 64-index block into the K ring -- prefill: four warps of 16-byte cp.async copies that arrive on the
+// landing barrier by hardware; FP8 decode: two groups of four warps that read the 656-byte records into registers,
+// de-quantise them once per pair and store them in the layout TMA would produce.  The V operand (64 tokens x 256
+// columns per CTA) is not read from global memory at all: the thread of warp 6 forwards it out of the landed K rows
+// with eight 4 KB cp.async.bulk shared-memory copies, four into its own V stage and four into the peer's
+// (distributed shared memory).  That thread also relays K landings to the leader and loads Q.  Invalid indices
+// leave zero rows and reach the softmax as validity bits.
+//
 // Semantics follow csrc/sm90/decode/dense/splitkv_mla.cu:948-957, 1022-1042, 1237-1269 of the reference
-// (borders, split outputs, LSE conventions).  Every wait is bounded; on expiry the pair drains and frees
+// (borders, split outputs, LSE conventions), csrc/sm100/decode/sparse_fp8 and csrc/sm100/prefill/sparse for the
+// index handling of the sparse modes.  Every wait is bounded; on expiry the pair drains and frees
 // its tensor memory.
 #include "kernels.h"
 #include "mla_work.cuh"
