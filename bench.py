@@ -132,10 +132,16 @@ def out_bound(ref_out) -> float:
 
 
 def _errs(out, ref_out, lse=None, ref_lse=None):
+    """Largest absolute errors against the oracle; a NaN anywhere counts as an infinite error (it would otherwise
+    vanish in a `max()` with an earlier finite value)."""
     from oracle.check import max_abs_diff
-    d = {"out_max_abs": max_abs_diff(out, ref_out), "out_bound": out_bound(ref_out)}
+
+    def err(a, b):
+        e = max_abs_diff(a, b)
+        return e if e == e else float("inf")
+    d = {"out_max_abs": err(out, ref_out), "out_bound": out_bound(ref_out)}
     if lse is not None:
-        d["lse_max_abs"] = max_abs_diff(lse, ref_lse)
+        d["lse_max_abs"] = err(lse, ref_lse)
     return d
 
 
