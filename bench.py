@@ -461,6 +461,7 @@ class SparsePrefill(Workload):
     bound = "tensor"
     key = "sparse_prefill"
     kernel_name = "mla_pair_kernel<prefill>"
+    e2e_buffers = 2
     launches_per_step = 1
     scaling = "strong"
     sharding = "query tokens sharded (kv replicated), no collective"
@@ -1021,7 +1022,7 @@ class Runner:
             r["e2e"] = {"value": units / (e_ms * 1e-3) / unit_scale(wl), "unit": wl.unit, "ms_per_step": e_ms, "steps": e_steps,
                         "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "note": "every step copies its inputs from pinned host memory and reads its results back; "
-                                + ("copies and kernels of neighbouring steps overlap (3 streams, 2 buffer sets); " if wl.e2e_buffers > 1 else "")
+                                + (f"copies and kernels of neighbouring steps overlap (3 streams, {wl.e2e_buffers} buffer sets); " if wl.e2e_buffers > 1 else "")
                                 + "the KV cache / kv tensor is resident device state"}
             if headline:
                 c_ms = self.e2e(wl, e_steps, run_kernel=False)
