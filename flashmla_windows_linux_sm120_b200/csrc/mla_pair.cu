@@ -128,6 +128,18 @@ __device__ __forceinline__ void pst_shared_v4(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// 32 bytes to global memory: one 256-bit store when the address allows it, else two 128-bit stores
+__device__ __forceinline__ void st_global_32B(void* p, const uint32_t (&w)[8]) {
+  if ((reinterpret_cast<uintptr_t>(p) & 31u) == 0) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]),
+                 "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+  } else {
+    reinterpret_cast<uint4*>(p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<uint4*>(p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+
 __device__ __forceinline__ void mma_pair_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
@@ -932,33 +944,40 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
           : reinterpret_cast<__nv_bfloat16*>(p.out) + r.batch * p.o_stride_b + tile.sq * p.o_stride_s + head * p.o_stride_h;
       const int64_t part_row = PREFILL ? 0 : ((int64_t)r.split_slot * p.h_k + tile.kh) * q_seq_per_hk + row_in_group;
       float* o_part = PREFILL ? nullptr : p.o_accum + part_row * 512;
-#pragma unroll 1
+      // The read of chunk c + 1 is in flight while chunk c is scaled and stored (two register sets), and every store
+      // is one full 32-byte sector per thread (each thread writes its own row, so the rows of a warp instruction are
+      // 1 KB or 2 KB apart: with 16-byte stores the load/store unit handled twice as many half-filled sectors).
+      constexpr int kSets = WM == kSparseDecode ? 1 : 2;      // the FP8 decode (480 threads, 128 registers) has no room for a second set
+      uint32_t ov[kSets][32];
+      if (have_o && kSets == 2) tc::tmem_ld32(tmem + lane_addr + TMEM_O, ov[0]);
+#pragma unroll 2
       for (int c = 0; c < 8; ++c) {
-        uint32_t ov[32];
+        uint32_t* cur = ov[c % kSets];
         if (have_o) {
-          tc::tmem_ld32(tmem + lane_addr + TMEM_O + c * 32, ov);
+          if constexpr (kSets == 1) tc::tmem_ld32(tmem + lane_addr + TMEM_O + c * 32, ov[0]);
           tc::tmem_wait_ld();
+          if (kSets == 2 && c + 1 < 8) tc::tmem_ld32(tmem + lane_addr + TMEM_O + (c + 1) * 32, ov[(c + 1) % kSets]);
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ov[i] = 0u;
+          for (int i = 0; i < 32; ++i) cur[i] = 0u;
         }
         const int col = (c >> 2) * 256 + th * 128 + (c & 3) * 32;
         if (r.no_split) {
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 v;
-            v.x = pack_16x2<F16>(__uint_as_float(ov[q4 * 8 + 0]) * inv, __uint_as_float(ov[q4 * 8 + 1]) * inv);
-            v.y = pack_16x2<F16>(__uint_as_float(ov[q4 * 8 + 2]) * inv, __uint_as_float(ov[q4 * 8 + 3]) * inv);
-            v.z = pack_16x2<F16>(__uint_as_float(ov[q4 * 8 + 4]) * inv, __uint_as_float(ov[q4 * 8 + 5]) * inv);
-            v.w = pack_16x2<F16>(__uint_as_float(ov[q4 * 8 + 6]) * inv, __uint_as_float(ov[q4 * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(o_final + col + q4 * 8) = v;
+          for (int q8 = 0; q8 < 2; ++q8) {
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              w[i] = pack_16x2<F16>(__uint_as_float(cur[q8 * 16 + 2 * i]) * inv, __uint_as_float(cur[q8 * 16 + 2 * i + 1]) * inv);
+            st_global_32B(o_final + col + q8 * 16, w);
           }
         } else {
 #pragma unroll
-          for (int q4 = 0; q4 < 8; ++q4) {
-            float4 v = make_float4(__uint_as_float(ov[q4 * 4 + 0]) * inv, __uint_as_float(ov[q4 * 4 + 1]) * inv,
-                                   __uint_as_float(ov[q4 * 4 + 2]) * inv, __uint_as_float(ov[q4 * 4 + 3]) * inv);
-            *reinterpret_cast<float4*>(o_part + col + q4 * 4) = v;
+          for (int q8 = 0; q8 < 4; ++q8) {
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] = __float_as_uint(__uint_as_float(cur[q8 * 8 + i]) * inv);
+            st_global_32B(o_part + col + q8 * 8, w);
           }
         }
       }
