@@ -17,8 +17,8 @@
 // the CTA's Q tile (tcgen05.cp from shared memory, rows duplicated into both lane halves as an M=64-per-CTA
 // A operand wants them), so only chunks 6..8 (24 KB) stay in shared memory -- that is what makes room for
 // the third K stage -- and the S instructions that take A from tensor memory run at 18 instead of 25 clocks.
-// The six chunks pass through the V ring on their way (free between the last P V of a request and the first of
-// the next); the K loads depend on nothing but the K ring and run ahead into the next request.
+// The six chunks pass through the V ring on their way for a CTA's first request and, three at a time, through the
+// Q area itself for every later one; the K loads depend on nothing but the K ring and run ahead into the next request.
 //
 //   warps 0-3 softmax : as in mla_tc.cu (TMEM lane = row + 64 * (token >= 32)); arrivals that the issuing
 //                       thread waits for go to the leader's barriers (remote arrive from rank 1)
