@@ -17,8 +17,8 @@
 // the CTA's Q tile (tcgen05.cp from shared memory, rows duplicated into both lane halves as an M=64-per-CTA
 // A operand wants them), so only chunks 6..8 (24 KB) stay in shared memory -- that is what makes room for
 // the third K stage -- and the S instructions that take A from tensor memory run at 18 instead of 25 clocks.
-// The six chunks pass through the V ring on their way for a CTA's first request and, three at a time, through the
-// Q area itself for every later one; the K loads depend on nothing but the K ring and run ahead into the next request.
+// The six chunks pass through the V ring on their way (free between the last P V of a request and the first of
+// the next); the K loads depend on nothing but the K ring and run ahead into the next request.
 //
 //   warps 0-3 softmax : as in mla_tc.cu (TMEM lane = row + 64 * (token >= 32)); arrivals that the issuing
 //                       thread waits for go to the leader's barriers (remote arrive from rank 1)
@@ -250,24 +250,6 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
   tc::tc_fence_after();
   pdl_allow_dependents();      // a merge kernel launched as a programmatic dependent may become resident now
   const uint32_t tmem = *sTmem;
-  // Q of a request (9 column chunks of 64 heads x 64 columns) reaches the CTA in one of two ways.  First request
-  // of the CTA: one load, chunks 0..5 staged in the (still unused) V ring, chunks 6..8 at their place.  Later
-  // requests: three loads of three chunks through the Q area itself (free as soon as the last S of the previous
-  // request has completed, well before its last P V releases the V ring); after each of the first two the leader
-  // copies the three chunks into tensor memory.  Phase -1 = the single load, 0..2 = the three loads.
-  auto issue_q_phase = [&](int phase, int c2, int c3) {
-    const uint32_t q_bar = rank == 0 ? bar(Q_FULL) : bar(Q_LAND);
-    if (phase < 0) {
-      tc::mbar_arrive_expect_tx(q_bar, kQBytes);
-#pragma unroll
-      for (int c = 0; c < 9; ++c)
-        tc::tma_load_4d(c < kQTmemChunks ? sV + c * kChunkBytes : sQ + (c - kQTmemChunks) * kChunkBytes, &tmap_q, c * 64, tile.head0, c2, c3, q_bar);
-    } else {
-      tc::mbar_arrive_expect_tx(q_bar, 3 * kChunkBytes);
-#pragma unroll
-      for (int c = 0; c < 3; ++c) tc::tma_load_4d(sQ + c * kChunkBytes, &tmap_q, (phase * 3 + c) * 64, tile.head0, c2, c3, q_bar);
-    }
-  };
 
   if (misaligned) {
     // nothing was issued; fall through to the common exit
@@ -542,7 +524,6 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
       skip_empty();
       enum { kNeedQ, kWaitQt, kForward };
       int state = kNeedQ, idle = 0;
-      int qph = -1, qt = 0;             // Q load phase in progress, commits of tensor-memory copies seen so far
       bool alive = true;
       auto v_empty_after = [&](int gg) { return tc::mbar_test_wait(bar(V_EMPTY0 + (gg & 1)), (gg >> 1) & 1); };   // P V of block gg has completed
       while (alive && (kg < total || wi < tile.n_work)) {
@@ -556,24 +537,22 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         }
         if (wi < tile.n_work) {
           if (state == kNeedQ) {
-            // every S of the previous request has completed: Q in shared and tensor memory is free
-            if (tc::mbar_test_wait(bar(Q_EMPTY), (req & 1) ^ 1)) {
-              qph = req == 0 ? -1 : 0;
-              issue_q_phase(qph, PREFILL ? r.batch : tile.sq, PREFILL ? 0 : r.batch);
+            // every S of the previous request has completed (Q in shared and tensor memory free) and its last two
+            // P V have released the V stages the new Q is staged in
+            if (tc::mbar_test_wait(bar(Q_EMPTY), (req & 1) ^ 1) && (vg < 1 || v_empty_after(vg - 1)) && (vg < 2 || v_empty_after(vg - 2))) {
+              const uint32_t q_bar = rank == 0 ? bar(Q_FULL) : bar(Q_LAND);
+              tc::mbar_arrive_expect_tx(q_bar, kQBytes);
+#pragma unroll
+              for (int c = 0; c < 9; ++c)
+                tc::tma_load_4d(c < kQTmemChunks ? sV + c * kChunkBytes : sQ + (c - kQTmemChunks) * kChunkBytes, &tmap_q, c * 64, tile.head0,
+                                PREFILL ? r.batch : tile.sq, PREFILL ? 0 : r.batch, q_bar);
               state = kWaitQt;
               did = true;
             }
           } else if (state == kWaitQt) {
-            if (tc::mbar_test_wait(bar(QT_DONE), qt & 1)) {        // in both CTAs: the commit goes to both
-              ++qt;
-              if (qph >= 0 && qph < 2) {
-                ++qph;
-                issue_q_phase(qph, PREFILL ? r.batch : tile.sq, PREFILL ? 0 : r.batch);
-              }
-              if (qph < 0 || qph == 2) {
-                ++req;
-                state = kForward;
-              }
+            if (tc::mbar_test_wait(bar(QT_DONE), req & 1)) {       // in both CTAs: the commit goes to both
+              ++req;
+              state = kForward;
               did = true;
             }
           } else if (vg < kg && (vg < 2 || v_empty_after(vg - 2))) {
@@ -626,26 +605,23 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     if (tc::elect_one()) {
       tc::prefetch_tensormap(&tmap_q);
       tc::prefetch_tensormap(&tmap_v64);
-      int g = 0, req = 0, qt = 0;
+      int g = 0, req = 0;
       bool alive = true;
       for (int wi = 0; wi < tile.n_work && alive; ++wi) {
         const Work r = get_work<WM>(P, tile, wi);
         if (r.blk_hi == r.blk_lo) continue;
         alive = tc::mbar_wait(bar(Q_EMPTY), (req & 1) ^ 1, status, 101);
+        for (int gg = max(0, g - 2); gg < g && alive; ++gg) alive = tc::mbar_wait(bar(V_EMPTY0 + (gg & 1)), (gg >> 1) & 1, status, 103);
         if (!alive) break;
-        if (req == 0) {
-          issue_q_phase(-1, tile.sq, r.batch);
-          alive = tc::mbar_wait(bar(QT_DONE), qt & 1, status, 107);       // the V ring may be filled
-          ++qt;
-        } else {
-          for (int ph = 0; ph < 3 && alive; ++ph) {
-            issue_q_phase(ph, tile.sq, r.batch);
-            if (ph < 2) {
-              alive = tc::mbar_wait(bar(QT_DONE), qt & 1, status, 107);   // the Q area may take the next three chunks
-              ++qt;
-            }
-          }
+        {
+          const uint32_t q_bar = rank == 0 ? bar(Q_FULL) : bar(Q_LAND);
+          tc::mbar_arrive_expect_tx(q_bar, kQBytes);
+#pragma unroll
+          for (int c = 0; c < 9; ++c)
+            tc::tma_load_4d(c < kQTmemChunks ? sV + c * kChunkBytes : sQ + (c - kQTmemChunks) * kChunkBytes, &tmap_q, c * 64, tile.head0,
+                            tile.sq, r.batch, q_bar);
         }
+        alive = tc::mbar_wait(bar(QT_DONE), req & 1, status, 107);       // the V ring may be refilled
         if (!alive) break;
         ++req;
         const int* bt = p.block_table + r.batch * p.block_table_stride_b;
@@ -702,16 +678,14 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     }
   } else if (warp == 5 && rank != 0) {
     // ================================ Q / K relay (peer only) ==========================
-    int g = 0, req = 0, qf = 0;
+    int g = 0, req = 0;
     bool alive = true;
     for (int wi = 0; wi < tile.n_work && alive; ++wi) {
       const Work r = get_work<WM>(P, tile, wi);
       if (r.blk_hi == r.blk_lo) continue;
-      for (int ph = 0; ph < (req == 0 ? 1 : 3) && alive; ++ph, ++qf) {       // one load for the first request, three later
-        alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_LAND), qf & 1, status, 111));
-        if (alive && lane == 0) tc::mbar_arrive_cluster(lbar(Q_FULL));
-      }
+      alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(Q_LAND), req & 1, status, 111));
       if (!alive) break;
+      if (lane == 0) tc::mbar_arrive_cluster(lbar(Q_FULL));
       for (int blk = r.blk_lo; blk < r.blk_hi && alive && !SPARSE; ++blk, ++g) {      // sparse modes: warp 6 relays K
         const int st = g % kKStages;
         alive = __all_sync(0xffffffffu, tc::mbar_wait(bar(K_LAND0 + st), (g / kKStages) & 1, status, 112));
@@ -734,7 +708,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         tc::tc_commit_pair(bar(b));
         tc::tc_commit_pair(tc::mapa(bar(b), 1));
       };
-      int g = 0, req = 0, qf = 0;       // qf: Q load phases waited for so far
+      int g = 0, req = 0;
       bool alive = true;
 #ifdef FMLA_TRACE
       int seen_k = -1, seen_s = -1, seen_p = -1, seen_v = -1, after_issue = 0;
@@ -743,32 +717,19 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
         const Work r = get_work<WM>(P, tile, wi);
         const int nblk = r.blk_hi - r.blk_lo;
         if (nblk == 0) continue;
-        // Q chunks 0..5: shared memory -> tensor memory of both CTAs (8 copies of 64 rows x 16 bytes per chunk), all
-        // six from the V ring for the first request, three at a time from the Q area later
-        for (int ph = 0; ph < (req == 0 ? 1 : 3) && alive; ++ph, ++qf) {
-          alive = __all_sync(0xffffffffu, tc::mbar_wait_cluster(bar(Q_FULL), qf & 1, status, 105));
-          if (!alive) break;
-          if (ph == 2) continue;          // chunks 6..8 stay in shared memory
-          tc::tc_fence_after();
-          if (tc::elect_one()) {
-            if (req == 0) {
-#pragma unroll
-              for (int c = 0; c < kQTmemChunks; ++c)
-#pragma unroll
-                for (int sub = 0; sub < 8; ++sub)
-                  tmem_cp_pair_64x128b(tmem + TMEM_Q + c * 32 + sub * 4, tc::desc_advance(desc_qstage, c * kChunkBytes + sub * 16));
-            } else {
-#pragma unroll
-              for (int c = 0; c < 3; ++c)
-#pragma unroll
-                for (int sub = 0; sub < 8; ++sub)
-                  tmem_cp_pair_64x128b(tmem + TMEM_Q + (ph * 3 + c) * 32 + sub * 4, tc::desc_advance(desc_q, c * kChunkBytes + sub * 16));
-            }
-            commit_both(QT_DONE);
-          }
-          __syncwarp();
-        }
+        alive = __all_sync(0xffffffffu, tc::mbar_wait_cluster(bar(Q_FULL), req & 1, status, 105));
         if (!alive) break;
+        // Q chunks 0..5: shared memory -> tensor memory of both CTAs (8 copies of 64 rows x 16 bytes per chunk)
+        tc::tc_fence_after();
+        if (tc::elect_one()) {
+#pragma unroll
+          for (int c = 0; c < kQTmemChunks; ++c)
+#pragma unroll
+            for (int sub = 0; sub < 8; ++sub)
+              tmem_cp_pair_64x128b(tmem + TMEM_Q + c * 32 + sub * 4, tc::desc_advance(desc_qstage, c * kChunkBytes + sub * 16));
+          commit_both(QT_DONE);
+        }
+        __syncwarp();
         // One poll reads every barrier of interest, one per lane:
         //   lane 0 P_FULL(jp)  lane 1 O_EMPTY  lane 2 V_FULL(jp)  lane 3 S_EMPTY(js)  lane 4 K_FULL(js)
         int js = 0, jp = 0, idle = 0;
