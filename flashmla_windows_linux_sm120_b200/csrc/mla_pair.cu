@@ -35,8 +35,8 @@
 // 0..5 = [320,512) (32 columns each); O / S layouts as in mla_tc.cu (the 64-row halves of an M=128 pair
 // instruction have the layout of the M=64 .ws form).
 //
-// Gathering modes (sparse FP8 decode: 480 threads, sparse prefill: 352 threads).  Each CTA brings only its 32 token
-// rows of a 64-index block into the K ring -- prefill: four warps of 16-byte cp.async copies that arrive on the
+// Gathering modes (sparse FP8 decode: 480 threads, sparse prefill: 320 threads).  Each CTA brings only its 32 token
+// rows of a 64-index block into the K ring -- prefill: three warps of 16-byte cp.async copies that arrive on the
 // landing barrier by hardware; FP8 decode: two groups of four warps that read the 656-byte records into registers,
 // de-quantise them once per pair and store them in the layout TMA would produce.  The V operand (64 tokens x 256
 // columns per CTA) is not read from global memory at all: the thread of warp 6 forwards it out of the landed K rows
@@ -88,9 +88,9 @@ static_assert(NUM_BARS * 8 <= 256, "barrier area too small");
 constexpr float kRescaleThreshold = 8.0f;
 constexpr int kThreads = 256;
 #ifndef FMLA_GATHER_WARPS
-#define FMLA_GATHER_WARPS 4
+#define FMLA_GATHER_WARPS 3
 #endif
-constexpr int kGatherWarps = FMLA_GATHER_WARPS;                 // sparse prefill: warp 4 and warps 8 .. 6 + kGatherWarps
+constexpr int kGatherWarps = FMLA_GATHER_WARPS;                 // sparse prefill: warp 4 and warps 8 .. 6 + kGatherWarps (measured: 3 -> 993, 4 -> 983, 5 -> 935, 2 -> 452 TFLOP/s)
 constexpr int kPrefillThreads = (7 + kGatherWarps) * 32;
 #ifndef FMLA_DECODE_GROUPS
 #define FMLA_DECODE_GROUPS 2
@@ -238,7 +238,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     // and a K stage has landed when every lane of the gather warps has arrived by hardware, plus the thread that
     // published the validity bits (prefill), or when every gather warp has stored its rows (FP8 decode)
     for (int i = Q_EMPTY; i < NUM_BARS; ++i)
-      tc::mbar_init(bar(i), !SPARSE ? 1 : (i >= K_EMPTY0 && i <= K_EMPTY2) ? 3 : (i >= K_LAND0 && i <= K_LAND2) ? (PREFILL ? kGatherWarps * 32 + 1 : kGatherWarps) : 1);
+      tc::mbar_init(bar(i), !SPARSE ? 1 : (i >= K_EMPTY0 && i <= K_EMPTY2) ? 3 : (i >= K_LAND0 && i <= K_LAND2) ? (PREFILL ? kGatherWarps * 32 + 1 : 4 /* FP8 decode: the four gather warps of a group */) : 1);
     tc::fence_mbar_init();
     *sAbort = 0;
     if (misaligned) tc::report_status(status, 30);
@@ -255,8 +255,8 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     // nothing was issued; fall through to the common exit
   } else if ((warp == 4 || warp >= 8) && WM == kSparsePrefill) {
     // ================================ Q and K loader, sparse prefill ===================
-    // The CTA's 32 token rows of a block (32 x 1152 bytes) are gathered with 16-byte cp.async copies by four warps
-    // (4, 8, 9, 10): 72 warp instructions per block, 18 per warp, consecutive lanes on consecutive pieces of a row.
+    // The CTA's 32 token rows of a block (32 x 1152 bytes) are gathered with 16-byte cp.async copies by three warps
+    // (4, 8, 9): 72 warp instructions per block, dealt out round robin, consecutive lanes on consecutive pieces of a row.
     // A warp keeps only a bounded number of such copies in flight: measured at the benchmark shape, three gather
     // warps gave 751 TFLOP/s, four 955-970, five 956, six 920, eight 930.  The TMA engine (tile::gather4, 4 rows x 64
     // columns per copy) gathers no faster than ~11 bytes per clock and SM, and mixing the two paths was slower
