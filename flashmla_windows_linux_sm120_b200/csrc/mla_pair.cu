@@ -257,8 +257,8 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
     // ================================ Q and K loader, sparse prefill ===================
     // The CTA's 32 token rows of a block (32 x 1152 bytes) are gathered with 16-byte cp.async copies by three warps
     // (4, 8, 9): 72 warp instructions per block, dealt out round robin, consecutive lanes on consecutive pieces of a row.
-    // A warp keeps only a bounded number of such copies in flight: measured at the benchmark shape, three gather
-    // warps gave 751 TFLOP/s, four 955-970, five 956, six 920, eight 930.  The TMA engine (tile::gather4, 4 rows x 64
+    // Measured at the benchmark shape: with each warp taking a contiguous third of the instructions 751 TFLOP/s; with
+    // the round-robin deal two warps 452, three 979-1009, four 964-982, five 935-957.  The TMA engine (tile::gather4, 4 rows x 64
     // columns per copy) gathers no faster than ~11 bytes per clock and SM, and mixing the two paths was slower
     // than either (8 of the 32 rows by TMA: 545 TFLOP/s; 16: 466), because the gathers queue behind the forwarding
     // copies in the TMA engine.  Each lane's copies arrive on the landing barrier by hardware (arrive.noinc).
