@@ -30,6 +30,7 @@ class DecodeParams(C.Structure):
         ("profile_event_begin", vp), ("profile_event_end", vp),
         ("indices_logical", i32),
         ("arrival_counters", vp),
+        ("no_split_hint", i32),
     ]
 
 

@@ -240,6 +240,7 @@ static int decode_impl(const fmla_decode_params* P, const fmla_peer_push* push, 
   k.out = a.out; k.o_stride_b = a.o_stride_b; k.o_stride_s = a.o_stride_s; k.o_stride_h = a.o_stride_h;
   k.softmax_lse = a.softmax_lse; k.lse_accum = a.lse_accum; k.o_accum = a.o_accum;
   k.arrival_counters = (!push && !sparse) ? a.arrival_counters : nullptr;
+  k.no_split_hint = (!push && a.no_split_hint) ? 1 : 0;
   if (push) {
     k.force_partial = 1;
     k.push_slot = push->slot; k.push_num_dst = push->num_dst; k.push_epoch = push->epoch; k.push_counter = push->counter;
@@ -262,6 +263,8 @@ static int decode_impl(const fmla_decode_params* P, const fmla_peer_push* push, 
     e = fmla::launch_decode_combine_push(k, s);
   } else if (!sparse && fmla::decode_dense_merges_in_kernel(k)) {
     e = cudaSuccess;      // the last CTA to deliver a partial of a request has merged it
+  } else if (k.no_split_hint) {
+    e = cudaSuccess;      // no request is split: every output is final already
   } else {
     e = fmla::launch_decode_combine(k, s);
   }

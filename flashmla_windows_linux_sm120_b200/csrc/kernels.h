@@ -39,6 +39,7 @@ struct DecodeKernelParams {
   int force_partial;
   int l2_prefetch_dist;        // pair kernel: cache pages this many blocks ahead are pulled into L2 (0 = off)
   int* arrival_counters;       // pair kernel: per (request, query token, 64-head tile) arrivals of split partials; zero on entry and exit
+  int no_split_hint;           // the caller states that no request is split: no merge kernel follows; a split request is reported (status 41)
   int push_slot, push_num_dst;
   float* push_o[8];            // [num_slots][b * h_k * rows][512]
   float* push_lse[8];          // [num_slots][b * h_k * rows], base 2

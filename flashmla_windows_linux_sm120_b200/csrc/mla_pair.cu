@@ -999,6 +999,7 @@ mla_pair_kernel(const __grid_constant__ TcParams P, const __grid_constant__ CUte
           p.softmax_lse[((int64_t)r.batch * p.h_q + head) * p.s_q + tile.sq] = inv == 0.f ? pos_inf() : (log2f(l) + m_used) * kLn2;
         } else {
           p.lse_accum[part_row] = inv == 0.f ? neg_inf() : log2f(l) + m_used;
+          if (p.no_split_hint && tid == 0) tc::report_status(status, 41);     // a split request although the caller ruled it out
         }
       }
       // ---- merge of a split request by whoever delivers its last partial ----------------

@@ -157,11 +157,26 @@ def fwd_kvcache_mla(q: torch.Tensor, kcache: torch.Tensor, head_size_v: int, seq
             merge_in_kernel = _MERGE_IN_KERNEL_DEFAULT
         if merge_in_kernel and not sparse and (h_q // h_k) % 128 == 0:
             p.arrival_counters = _counters_for(q, b * s_q * (h_q // 64)).data_ptr()
+        p.no_split_hint = int(_no_request_is_split(num_splits, b))
         if profile_events is not None:
             p.profile_event_begin = profile_events[0].cuda_event
             p.profile_event_end = profile_events[1].cuda_event
         check(lib.fmla_fwd_kvcache_mla(C.byref(p), _stream(q)))
     return [out, lse]
+
+
+def _no_request_is_split(num_splits: torch.Tensor, b: int) -> bool:
+    """True when the schedule gives every request to one partition (num_splits[b] == b): the merge kernel is then
+    not launched.  Read back from the device once per metadata tensor (one synchronisation, remembered on the
+    tensor object; a decode step reuses its metadata for every layer); unknown -- and therefore False -- while the
+    stream is being captured into a CUDA graph before that first read."""
+    known = getattr(num_splits, "_fmla_no_split", None)
+    if known is None:
+        if torch.cuda.is_current_stream_capturing():
+            return False
+        known = bool(int(num_splits[b].item()) == b)
+        num_splits._fmla_no_split = known
+    return known
 
 
 def sparse_prefill_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: float,

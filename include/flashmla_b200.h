@@ -133,6 +133,12 @@ typedef struct fmla_decode_params {
    * one kernel.  Calls that may overlap on the GPU need separate counter arrays.  NULL = the merge runs as a
    * second kernel (fmla's counterpart of csrc/smxx/mla_combine.cu).  No counterpart in the reference. */
   int32_t* arrival_counters;
+
+  /* optional: non-zero = the caller knows that the schedule splits no request (num_splits[b] == b), so every
+   * partition writes final outputs and the merge kernel has nothing to do: it is not launched.  A kernel that
+   * meets a split request under this hint reports status 41 instead of leaving partials unmerged.  0 = unknown
+   * (the merge kernel is launched and finds out by itself).  No counterpart in the reference. */
+  int32_t no_split_hint;
 } fmla_decode_params;
 
 /* Bytes of lse_accum and o_accum for a problem (host-side arithmetic only). */

@@ -229,3 +229,57 @@ def test_dense_decode_merge_in_kernel_is_bit_equal_to_the_merge_kernel(s_q):
         assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1])
     r_out, r_lse = decode.decode_ref(d.cache_seqlens, d.block_table, d.q, d.blocked_k, 512, True)
     U.assert_out_lse(got[0].cpu(), got[1].cpu(), r_out, r_lse, what=f"merge in kernel s_q={s_q}")
+
+
+def _device_status(reset=True):
+    import ctypes as C
+
+    from flashmla_windows_linux_sm120_b200._cabi import lib
+    st = C.c_int(0)
+    rc = lib.fmla_device_status(C.byref(st), int(reset))
+    return rc, st.value
+
+
+@pytest.mark.parametrize("h_q,b", [(128, 21), (64, 42)])
+def test_no_merge_kernel_when_no_request_is_split(h_q, b):
+    """Requests of equal cost (2 blocks + 5 of overhead) whose number makes the pitch of the cuts equal to that
+    cost: the schedule splits none of them, the binding reads that back once (remembered on the metadata tensor)
+    and the merge kernel is not launched.  Same results."""
+    fm = _api()
+    t = gen.DecodeCase(b=b, s_q=1, s_k=600, is_varlen=True, topk=128, h_q=h_q)
+    d = gen.make_decode_case(t)
+    kq = quant.quantize_k_cache(d.blocked_k, t.dv, 128)
+    kd = quant.dequantize_k_cache(kq)
+    lens = d.cache_seqlens.cuda()
+    md, ns = fm.get_mla_metadata(lens, t.s_q * t.h_q, 1, t.h_q, True, t.topk)
+    assert int(ns[t.b]) == t.b                      # no request is split
+    for _ in range(2):                              # the second call uses the remembered answer
+        out, lse = fm.flash_mla_with_kvcache(d.q.cuda(), kq.cuda(), d.block_table.cuda(), lens, t.dv, md, ns,
+                                             is_fp8_kvcache=True, indices=d.indices.cuda())
+        torch.cuda.synchronize()
+        assert ns._fmla_no_split is True
+        ref_out, ref_lse = decode.decode_ref(d.cache_seqlens, d.block_table, d.q, kd, t.dv, False, d.abs_indices)
+        U.assert_out_lse(out.cpu(), lse.cpu(), ref_out, ref_lse)
+    assert _device_status() == (0, 0)
+
+
+def test_a_wrong_no_split_hint_is_reported():
+    """A caller that rules out split requests although the schedule has some gets a device status, not silently
+    unmerged partials."""
+    fm = _api()
+    t = gen.DecodeCase(b=3, s_q=1, s_k=900, h_q=128, is_varlen=True)
+    d = gen.make_decode_case(t)
+    lens = d.cache_seqlens.cuda()
+    md, ns = fm.get_mla_metadata(lens, t.s_q * t.h_q, 1)
+    assert int(ns[t.b]) > t.b                       # some request is split
+    ns._fmla_no_split = True                        # what a stale or wrong answer would look like
+    fm.flash_mla_with_kvcache(d.q.cuda(), d.blocked_k.cuda(), d.block_table.cuda(), lens, t.dv, md, ns, causal=False)
+    torch.cuda.synchronize()
+    rc, code = _device_status(reset=True)
+    assert rc == 5 and code == 41
+    assert _device_status() == (0, 0)
+    ns._fmla_no_split = False
+    out, lse = fm.flash_mla_with_kvcache(d.q.cuda(), d.blocked_k.cuda(), d.block_table.cuda(), lens, t.dv, md, ns, causal=False)
+    torch.cuda.synchronize()
+    ref_out, ref_lse = decode.decode_ref(d.cache_seqlens, d.block_table, d.q, d.blocked_k, t.dv, False)
+    U.assert_out_lse(out.cpu(), lse.cpu(), ref_out, ref_lse)
